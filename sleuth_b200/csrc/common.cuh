@@ -248,7 +248,9 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 //   silu:           g * sigmoid(g) * u
 //   relu:           max(g, 0) * u
 //   clamped swish:  g' = min(g, limit), u' = clamp(u, -limit, limit);  g' * sigmoid(alpha * g') * (u' + 1)
-enum GateKind : int { kGateSilu = 0, kGateRelu = 1, kGateClampedSwish = 2 };
+//   tanh gelu:      0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u
+enum GateKind : int { kGateSilu = 0, kGateRelu = 1, kGateClampedSwish = 2, kGateGeluTanh = 3 };
+constexpr int kGateLast = kGateGeluTanh;
 struct GateAct {
   int kind;
   float limit, alpha;      // read by the clamped swish only
@@ -260,6 +262,7 @@ __device__ __forceinline__ float gated(const GateAct& a, float g, float u) {
     u = fminf(fmaxf(u, -a.limit), a.limit);
     return (g / (1.0f + expf(-a.alpha * g))) * (u + 1.0f);
   }
+  if (a.kind == kGateGeluTanh) return (0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))) * u;
   return (g / (1.0f + expf(-g))) * u;
 }
 

@@ -265,6 +265,91 @@ __global__ void stream_inject_kernel(float* __restrict__ x, const float* __restr
   }
 }
 
+// A hashed table of token pairs added to the embedding: x[t, :] += pairs[row(t), :] with
+// row = (previous token * mul_prev + token * mul_cur) mod buckets, and row = buckets (the table's last row) for a
+// sequence's first token. The previous token of a step's first token comes from last[slot], the sequence's state; the
+// block of that token then leaves the step's last token there for the next step (it alone reads and writes the entry).
+template <typename TW>
+__global__ void pair_embed_kernel(const int* __restrict__ ids, const int* __restrict__ map, const TW* __restrict__ pairs,
+                                  float* __restrict__ x, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                  const int* __restrict__ seq_start, const int* __restrict__ slots, int* __restrict__ last,
+                                  int dim, int vocab, int buckets, long long mul_prev, long long mul_cur) {
+  pdl_enter();
+  const int t = blockIdx.x;
+  const int seq = tok_seq[t];
+  const bool first = t == seq_start[seq];
+  int tok = ids[map ? map[t] : t];
+  tok = min(max(tok, 0), vocab - 1);
+  long long row = buckets;
+  if (tok_pos[t] > 0) {
+    int prev = first ? last[slots[seq]] : ids[map ? map[t - 1] : t - 1];
+    prev = min(max(prev, 0), vocab - 1);
+    row = (prev * mul_prev + tok * mul_cur) % buckets;
+    if (row < 0) row += buckets;
+  }
+  const TW* src = pairs + (size_t)row * dim;
+  float* out = x + (size_t)t * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] += to_f32(src[i]);
+  if (first && threadIdx.x == 0) {
+    const int e = seq_start[seq + 1] - 1;
+    last[slots[seq]] = min(max(ids[map ? map[e] : e], 0), vocab - 1);
+  }
+}
+
+// The end of a sublayer that is gated and normalised before it joins the stream:
+//   v = y * sigmoid(g + b) (g absent: v = y);  x += v / sqrt(mean(v^2) + eps) * w
+// y [T, dim] float32 (overwritten with v), g [T, dim] float32 with row stride g_stride, b and w [dim] float32.
+__global__ void gated_norm_add_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ g,
+                                      long long g_stride, const float* __restrict__ b, const float* __restrict__ w, int dim,
+                                      float eps) {
+  pdl_enter();
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  float* yr = y + (size_t)r * dim;
+  const float* gr = g ? g + (size_t)r * g_stride : nullptr;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float v = yr[i];
+    if (gr) {
+      const float z = gr[i] + (b ? b[i] : 0.0f);
+      v = v * (1.0f / (1.0f + expf(-z)));
+      yr[i] = v;
+    }
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  float* xr = x + (size_t)r * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) xr[i] += (yr[i] * inv) * w[i];
+}
+
+// out[t, :] = [a[t, :] | b[t, :]] in the run dtype: two float32 streams side by side as one product's input.
+template <typename TO>
+__global__ void stream_pair_kernel(const float* __restrict__ a, const float* __restrict__ b, TO* __restrict__ out, int dim,
+                                   size_t total) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    const size_t t = i / (2 * (size_t)dim), c = i - t * 2 * dim;
+    out[i] = from_f32<TO>(c < (size_t)dim ? a[t * dim + c] : b[t * dim + c - dim]);
+  }
+}
+
+// v *= factor, or with `add` [cols]: v = v * factor + add[col]; v float32 [rows, cols] with a row stride.
+__global__ void scale_kernel(float* __restrict__ v, long long row_stride, int cols, size_t total, float factor,
+                             const float* __restrict__ add) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    const size_t r = i / cols, c = i - r * cols;
+    float* p = v + r * row_stride + c;
+    *p = add ? fmaf(*p, factor, add[c]) : *p * factor;
+  }
+}
+
+
 static int norm_threads(int dim) {
   int t = 32;
   while (t < 512 && t * 4 < dim) t <<= 1;
@@ -361,11 +446,11 @@ extern "C" int slb_swiglu(const void* gu, void* act, int dtype, int tokens, int 
   return check_launch("swiglu");
 }
 
-// kind: 0 = silu (the kernels of slb_swiglu), 1 = relu, 2 = clamped swish with `limit` and `alpha` (common.cuh).
+// kind: 0 = silu (the kernels of slb_swiglu), 1 = relu, 2 = clamped swish with `limit` and `alpha`, 3 = tanh gelu (common.cuh).
 extern "C" int slb_gated_act(const void* gu, void* act, int dtype, int tokens, int inter, int kind, float limit, float alpha,
                              void* stream) {
   if (kind == kGateSilu) return slb_swiglu(gu, act, dtype, tokens, inter, stream);
-  SLB_REQUIRE(kind == kGateRelu || kind == kGateClampedSwish, "gated_act: unknown activation %d", kind);
+  SLB_REQUIRE(kind > kGateSilu && kind <= kGateLast, "gated_act: unknown activation %d", kind);
   SLB_REQUIRE(kind != kGateClampedSwish || limit > 0.0f, "gated_act: the clamp limit must be positive, got %g", (double)limit);
   SLB_REQUIRE(tokens >= 0 && inter > 0, "gated_act: tokens=%d inter=%d", tokens, inter);
   if (tokens == 0) return 0;
@@ -436,4 +521,60 @@ extern "C" int slb_stream_inject(float* x, const float* again, const float* row,
   if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
   launch(stream_inject_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, x, again, row, dim, total);
   return check_launch("stream_inject");
+}
+
+// x [tokens, dim] float32 already holds the tokens' own rows; pairs [buckets + 1, dim]; last: int32 [slots], one
+// entry per sequence slot (the sequence's last token so far).
+extern "C" int slb_pair_embed(const int* ids, const int* map, const void* pairs, int table_dtype, float* x, const int* tok_seq,
+                              const int* tok_pos, const int* seq_start, const int* slots, int* last, int tokens, int dim,
+                              int vocab, int buckets, long long mul_prev, long long mul_cur, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && dim > 0 && vocab > 0 && buckets > 0, "pair_embed: tokens=%d dim=%d vocab=%d buckets=%d", tokens, dim,
+              vocab, buckets);
+  SLB_REQUIRE(mul_prev >= 0 && mul_cur >= 0 && mul_prev < (1LL << 31) && mul_cur < (1LL << 31), "pair_embed: multipliers %lld, %lld",
+              mul_prev, mul_cur);
+  if (tokens == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = dim >= 256 ? 256 : 64;
+  if (table_dtype == kF32)
+    launch(pair_embed_kernel<float>, dim3(tokens), dim3(threads), 0, s, ids, map, (const float*)pairs, x, tok_seq, tok_pos, seq_start,
+           slots, last, dim, vocab, buckets, mul_prev, mul_cur);
+  else if (table_dtype == kBF16)
+    launch(pair_embed_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, s, ids, map, (const __nv_bfloat16*)pairs, x, tok_seq,
+           tok_pos, seq_start, slots, last, dim, vocab, buckets, mul_prev, mul_cur);
+  else
+    return fail(1, "pair_embed: unknown dtype %d", table_dtype);
+  return check_launch("pair_embed");
+}
+
+extern "C" int slb_gated_norm_add(float* x, float* y, const float* g, long long g_stride, const float* b, const float* w,
+                                  int rows, int dim, float eps, void* stream) {
+  SLB_REQUIRE(rows >= 0 && dim > 0 && eps > 0.0f && (g == nullptr || g_stride >= dim), "gated_norm_add: rows=%d dim=%d eps=%g", rows,
+              dim, (double)eps);
+  if (rows == 0) return 0;
+  launch(gated_norm_add_kernel, dim3(rows), dim3(norm_threads(dim)), 0, (cudaStream_t)stream, x, y, g, g_stride, b, w, dim, eps);
+  return check_launch("gated_norm_add");
+}
+
+extern "C" int slb_stream_pair(const float* a, const float* b, void* out, int out_dtype, int tokens, int dim, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && dim > 0, "stream_pair: tokens=%d dim=%d", tokens, dim);
+  SLB_REQUIRE(out_dtype == kF32 || out_dtype == kBF16, "stream_pair: unknown dtype %d", out_dtype);
+  if (tokens == 0) return 0;
+  const size_t total = (size_t)tokens * 2 * dim;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+  if (out_dtype == kF32)
+    launch(stream_pair_kernel<float>, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, a, b, (float*)out, dim, total);
+  else
+    launch(stream_pair_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, a, b, (__nv_bfloat16*)out, dim, total);
+  return check_launch("stream_pair");
+}
+
+extern "C" int slb_scale(float* v, long long row_stride, int rows, int cols, float factor, const float* add, void* stream) {
+  SLB_REQUIRE(rows >= 0 && cols > 0 && row_stride >= cols, "scale: rows=%d cols=%d stride=%lld", rows, cols, row_stride);
+  if (rows == 0) return 0;
+  const size_t total = (size_t)rows * cols;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+  launch(scale_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, v, row_stride, cols, total, factor, add);
+  return check_launch("scale");
 }

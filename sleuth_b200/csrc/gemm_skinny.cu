@@ -345,7 +345,7 @@ extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int
 extern "C" int slb_gemm_skinny_gated(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int kind,
                                      float limit, float alpha, const void* next, long long next_bytes,
                                      const NextPages* pages, int features, void* stream) {
-  SLB_REQUIRE(kind >= kGateSilu && kind <= kGateClampedSwish, "gemm_skinny: unknown activation %d", kind);
+  SLB_REQUIRE(kind >= kGateSilu && kind <= kGateLast, "gemm_skinny: unknown activation %d", kind);
   return skinny_run(X, W, C, M, N, K, ldc, kSwiglu, GateAct{kind, limit, alpha}, next, next_bytes, pages, features, stream);
 }
 

@@ -217,6 +217,10 @@ __device__ __forceinline__ float fast_silu(float g) { return __fdividef(g, 1.0f 
 // The other gated activations with the same fast exponential and division.
 __device__ __forceinline__ float fast_gated(const GateAct& f, float g, float u) {
   if (f.kind == kGateRelu) return fmaxf(g, 0.0f) * u;
+  if (f.kind == kGateGeluTanh) {      // 0.5 g (1 + tanh(t)) = g / (1 + exp(-2 t))
+    const float t = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return __fdividef(g, 1.0f + __expf(-2.0f * t)) * u;
+  }
   g = fminf(g, f.limit);
   u = fminf(fmaxf(u, -f.limit), f.limit);
   return __fdividef(g, 1.0f + __expf(-f.alpha * g)) * (u + 1.0f);
@@ -666,7 +670,7 @@ extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, 
 // The gated form (mode 3) with another activation than SiLU: kind, limit, alpha as in common.cuh.
 extern "C" int slb_gemm_tc_gated(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int kind, float limit,
                                  float alpha, int* status, void* stream) {
-  SLB_REQUIRE(kind >= kGateSilu && kind <= kGateClampedSwish, "gemm_tc: unknown activation %d", kind);
+  SLB_REQUIRE(kind >= kGateSilu && kind <= kGateLast, "gemm_tc: unknown activation %d", kind);
   return gemm_tc_run(X, W, C, M, N, K, ldc, kTcSwiglu, GateAct{kind, limit, alpha}, status, stream);
 }
 
@@ -725,7 +729,7 @@ extern "C" int slb_gemm_tc_grouped(const void* X, const void* W, void* C, int M,
 extern "C" int slb_gemm_tc_grouped_gated(const void* X, const void* W, void* C, int M, int N, int K, int groups, int mode,
                                          const int* group_tiles, int max_row_tiles, int kind, float limit, float alpha,
                                          int* status, void* stream) {
-  SLB_REQUIRE(kind >= kGateSilu && kind <= kGateClampedSwish, "gemm_tc_grouped: unknown activation %d", kind);
+  SLB_REQUIRE(kind >= kGateSilu && kind <= kGateLast, "gemm_tc_grouped: unknown activation %d", kind);
   SLB_REQUIRE(slb_gemm_tc_supported(M, N, K) && groups >= 1, "gemm_tc_grouped: M=%d N=%d K=%d groups=%d", M, N, K, groups);
   SLB_REQUIRE((mode == 0 || mode == 1 || mode == 3) && status != nullptr && group_tiles != nullptr && max_row_tiles >= 1,
               "gemm_tc_grouped: mode=%d", mode);

@@ -25,24 +25,25 @@ constexpr size_t kLatMaxSmem = 227 * 1024;      // dynamic shared memory a block
 constexpr int kLatWarps = 8;
 constexpr int kLatRowsPerWarp = kLatRows / kLatWarps;
 
-// One block per token. lat[t] = [q_rank | R | P] float32.
+// One block per token. lat[t] = [q_rank | R | P | anything] float32, rows `lat_stride` values apart; q_rank may be 0 (the
+// queries do not pass through a latent: nothing is written to cq).
 template <typename TO>
 __global__ void latent_post_kernel(const float* __restrict__ lat, const float* __restrict__ q_gain,
                                    const float* __restrict__ c_gain, const float* __restrict__ cos_t,
                                    const float* __restrict__ sin_t, TO* __restrict__ cq, TO* __restrict__ pool,
                                    const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                    const int* __restrict__ table, int stride, int q_rank, int R, int P, int rot,
-                                   float eps, TO* __restrict__ c_out, TO* __restrict__ k_out) {
+                                   float eps, TO* __restrict__ c_out, TO* __restrict__ k_out, int lat_stride) {
   pdl_enter();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
-  const float* row = lat + (size_t)t * (q_rank + R + P);
+  const float* row = lat + (size_t)t * lat_stride;
   float sq = 0.f, sc = 0.f;
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x) sq = fmaf(row[i], row[i], sq);
   for (int i = threadIdx.x; i < R; i += blockDim.x) sc = fmaf(row[q_rank + i], row[q_rank + i], sc);
-  sq = block_sum(sq, scratch);
+  if (q_rank > 0) sq = block_sum(sq, scratch);
   sc = block_sum(sc, scratch);
-  const float inv_q = 1.0f / sqrtf(sq / (float)q_rank + eps);
+  const float inv_q = q_rank > 0 ? 1.0f / sqrtf(sq / (float)q_rank + eps) : 0.0f;
   const float inv_c = 1.0f / sqrtf(sc / (float)R + eps);
   TO* qo = cq + (size_t)t * q_rank;
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x) qo[i] = from_f32<TO>((row[i] * inv_q) * q_gain[i]);
@@ -792,6 +793,22 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restri
   }
 }
 
+// One gate value per head: y[t, h * dv + j] = val[h, t, j] * sigmoid(g[t * g_stride + h]), g float32.
+template <typename T>
+__global__ void latent_head_gate_kernel(const T* __restrict__ val, const float* __restrict__ g, long long g_stride,
+                                        T* __restrict__ y, int Tn, int H, int dv, size_t total) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    const size_t t = i / ((size_t)H * dv);
+    const int rest = (int)(i - t * H * dv), h = rest / dv, j = rest - h * dv;
+    const float v = to_f32(val[((size_t)h * Tn + t) * dv + j]);
+    const float z = g[t * g_stride + h];
+    y[i] = from_f32<T>(v * (1.0f / (1.0f + expf(-z))));
+  }
+}
+
 // y[t, h * dv + j] = val[h, t, j] * sigmoid(g[t, h * dv + j])
 template <typename T>
 __global__ void latent_gate_kernel(const T* __restrict__ val, const T* __restrict__ g, T* __restrict__ y, int Tn, int H,
@@ -831,9 +848,12 @@ using namespace slb;
 extern "C" int slb_latent_post(const float* lat, const float* q_gain, const float* c_gain, const float* cos_t,
                                const float* sin_t, void* cq, void* pool, const int* tok_seq, const int* tok_pos,
                                const int* table, int stride, int tokens, int q_rank, int R, int P, int rot, float eps,
-                               int dtype, void* c_out, void* k_out, void* stream) {
-  SLB_REQUIRE(tokens >= 0 && q_rank > 0 && R > 0 && P >= 0 && rot >= 0 && rot <= P && rot % 2 == 0 && eps > 0.f,
+                               int dtype, void* c_out, void* k_out, int lat_stride, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && q_rank >= 0 && R > 0 && P >= 0 && rot >= 0 && rot <= P && rot % 2 == 0 && eps > 0.f,
               "latent_post: tokens=%d q_rank=%d rank=%d rot_dim=%d rotated=%d", tokens, q_rank, R, P, rot);
+  if (lat_stride <= 0) lat_stride = q_rank + R + P;
+  SLB_REQUIRE(lat_stride >= q_rank + R + P && (q_rank == 0 || cq != nullptr), "latent_post: rows of %d values hold %d + %d + %d",
+              lat_stride, q_rank, R, P);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "latent_post: unknown dtype %d", dtype);
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
@@ -841,11 +861,11 @@ extern "C" int slb_latent_post(const float* lat, const float* q_gain, const floa
   const int threads = widest > 512 ? 256 : (widest > 128 ? 128 : 64);
   if (dtype == kF32)
     launch(latent_post_kernel<float>, dim3(tokens), dim3(threads), 0, s, lat, q_gain, c_gain, cos_t, sin_t, (float*)cq,
-           (float*)pool, tok_seq, tok_pos, table, stride, q_rank, R, P, rot, eps, (float*)c_out, (float*)k_out);
+           (float*)pool, tok_seq, tok_pos, table, stride, q_rank, R, P, rot, eps, (float*)c_out, (float*)k_out, lat_stride);
   else
     launch(latent_post_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, s, lat, q_gain, c_gain, cos_t, sin_t,
            (__nv_bfloat16*)cq, (__nv_bfloat16*)pool, tok_seq, tok_pos, table, stride, q_rank, R, P, rot, eps, (__nv_bfloat16*)c_out,
-           (__nv_bfloat16*)k_out);
+           (__nv_bfloat16*)k_out, lat_stride);
   return check_launch("latent_post");
 }
 
@@ -1013,4 +1033,23 @@ extern "C" int slb_latent_gate(const void* val, const void* g, void* y, int toke
   else
     return fail(1, "latent_gate: unknown dtype %d", dtype);
   return check_launch("latent_gate");
+}
+
+// val [H, tokens, dv] and y [tokens, H * dv] in `dtype`; g float32, one value per (token, head), rows g_stride apart.
+extern "C" int slb_latent_head_gate(const void* val, const float* g, long long g_stride, void* y, int tokens, int H, int dv,
+                                    int dtype, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && H > 0 && dv > 0 && g_stride >= H, "latent_head_gate: tokens=%d heads=%d width=%d", tokens, H, dv);
+  if (tokens == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t total = (size_t)tokens * H * dv;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+  if (dtype == kF32)
+    launch(latent_head_gate_kernel<float>, dim3((int)blocks), dim3(256), 0, s, (const float*)val, g, g_stride, (float*)y, tokens, H, dv, total);
+  else if (dtype == kBF16)
+    launch(latent_head_gate_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, (const __nv_bfloat16*)val, g, g_stride,
+           (__nv_bfloat16*)y, tokens, H, dv, total);
+  else
+    return fail(1, "latent_head_gate: unknown dtype %d", dtype);
+  return check_launch("latent_head_gate");
 }

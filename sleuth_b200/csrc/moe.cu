@@ -108,6 +108,9 @@ __global__ void __launch_bounds__(256) moe_logits_few_kernel(const T* __restrict
 //              of its two largest scores (of its one score, if it has one expert); only experts of the `keep` best
 //              groups can be chosen. The `top` largest scores among them; weights = score / (sum of the chosen scores
 //              + 1e-20) * scale.
+//   scoring 2: scores = softmax(logits) over all experts; the `top` largest of score + pick_bias (a correction per expert
+//              that steers the choice only; absent = 0) are chosen; weights = the chosen experts' scores * scale, not
+//              renormalised.
 struct RouteRule {
   int scoring, groups, keep;
   float scale;
@@ -117,11 +120,13 @@ struct RouteRule {
 // share the row, four partial sums each, joined in a fixed order); warp 0 then picks the `top` largest.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr,
-                                                        const float* __restrict__ bias, const float* __restrict__ given,
-                                                        int* __restrict__ choice, float* __restrict__ weight, int tokens,
-                                                        int dim, int E, int top, RouteRule rule) {
+                                                        const float* __restrict__ bias, const float* __restrict__ pick_bias,
+                                                        const float* __restrict__ given, int* __restrict__ choice,
+                                                        float* __restrict__ weight, int tokens, int dim, int E, int top,
+                                                        RouteRule rule) {
   pdl_enter();
-  extern __shared__ float z[];         // [E], then [groups] group scores and [groups] flags when groups limit the choice
+  extern __shared__ float z[];         // [E], then [groups] group scores and [groups] flags when groups limit the choice,
+                                       // then (scoring 2) [E] choice scores
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const T* row = h + (size_t)t * dim;
@@ -184,12 +189,32 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
       if (!open[e / size]) z[e] = -INFINITY;
     __syncwarp();
   }
+  float* sel = z;                      // what the choice looks at
+  if (rule.scoring == 2) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float p = expf(z[e] - mx);
+      z[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    sel = z + E + 2 * rule.groups;
+    for (int e = lane; e < E; e += 32) {
+      const float sc = z[e] / sum;
+      z[e] = sc;
+      sel[e] = sc + (pick_bias ? pick_bias[e] : 0.f);
+    }
+    __syncwarp();
+  }
   float first = 0.f, mass = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int best_e = E;
     for (int e = lane; e < E; e += 32) {
-      const float v = z[e];
+      const float v = sel[e];
       if (v > best) { best = v; best_e = e; }
     }
 #pragma unroll
@@ -200,15 +225,17 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
     }
     best_e = min(best_e, E - 1);                 // only logits that are not numbers get here
     if (k == 0) first = best;
-    const float p = rule.scoring == 1 ? best : expf(best - first);
+    const float p = rule.scoring == 2 ? z[best_e] * rule.scale : (rule.scoring == 1 ? best : expf(best - first));
     mass += p;
+    __syncwarp();
     if (lane == 0) {
       choice[(size_t)t * top + k] = best_e;
       weight[(size_t)t * top + k] = p;
-      z[best_e] = -INFINITY;
+      sel[best_e] = -INFINITY;
     }
     __syncwarp();
   }
+  if (rule.scoring == 2) return;
   if (rule.scoring == 1) {
     for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] = weight[(size_t)t * top + k] / (mass + 1e-20f) * rule.scale;
   } else {
@@ -668,7 +695,7 @@ extern "C" int slb_moe_experts_tc(const void* h, const void* w_gu, const void* w
 // logits: float32 scratch [tokens, E], or null (then every token's block forms its own logits); with logits_ready they
 // hold the logits already (a matrix product formed them) and nothing is computed from h. tiles: int32
 // [1 + 3 * (tokens * top / 128 + min(tokens * top, E))] for the grouped tensor-memory product, or null.
-extern "C" int slb_moe_route(const void* h, const float* w_router, const float* bias, int* choice, float* weight,
+extern "C" int slb_moe_route(const void* h, const float* w_router, const float* bias, const float* pick_bias, int* choice, float* weight,
                              int* rank, int* counts, int* place, int* list, float* logits, int* tiles, int layout,
                              int tokens, int dim, int E, int top, int scoring, int groups, int keep, float route_scale,
                              int logits_ready, int dtype, void* stream) {
@@ -676,7 +703,8 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
               tokens, dim, E, top);
   SLB_REQUIRE(E <= 4096, "moe_route: at most 4096 experts, got %d", E);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "moe_route: unknown dtype %d", dtype);
-  SLB_REQUIRE(scoring == 0 || scoring == 1, "moe_route: unknown scoring %d", scoring);
+  SLB_REQUIRE(scoring >= 0 && scoring <= 2, "moe_route: unknown scoring %d", scoring);
+  SLB_REQUIRE(pick_bias == nullptr || scoring == 2, "moe_route: a choice correction goes with the softmax scoring over all experts");
   if (groups <= 0) groups = 1;
   if (keep <= 0 || keep > groups) keep = groups;
   SLB_REQUIRE(E % groups == 0, "moe_route: %d experts do not form %d equal groups", E, groups);
@@ -686,7 +714,7 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
   cudaStream_t s = (cudaStream_t)stream;
   (void)rank;      // kept in the signature: callers hand over a table that older versions filled
   const RouteRule rule{scoring, groups, keep, route_scale};
-  const size_t smem = (size_t)(E + 2 * groups) * sizeof(float);
+  const size_t smem = (size_t)(E + 2 * groups + (scoring == 2 ? E : 0)) * sizeof(float);
   const dim3 grid(tokens);
   // from a few tokens on the logits are formed 32 tokens and 16 experts at a time, each weight read once a block
   const float* given = nullptr;
@@ -711,9 +739,9 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
   // with the logits given only the choosing warp has work: a block of one warp, so that many tokens are resident at once
   const dim3 block(given != nullptr && tokens >= 256 ? 32 : 256);
   if (dtype == kF32)
-    launch(moe_route_kernel<float>, grid, block, smem, s, (const float*)h, w_router, bias, given, choice, weight, tokens, dim, E, top, rule);
+    launch(moe_route_kernel<float>, grid, block, smem, s, (const float*)h, w_router, bias, pick_bias, given, choice, weight, tokens, dim, E, top, rule);
   else
-    launch(moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, w_router, bias, given, choice, weight,
+    launch(moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, w_router, bias, pick_bias, given, choice, weight,
            tokens, dim, E, top, rule);
   int rc = check_launch("moe_route");
   if (rc || !layout) return rc;        // a step of few pairs needs no counts and no expert order
@@ -733,7 +761,7 @@ extern "C" int slb_moe_experts(const void* h, const void* w_gu, const void* w_do
   SLB_REQUIRE(tokens >= 0 && dim > 0 && ff > 0 && E > 0 && top > 0, "moe_experts: tokens=%d dim=%d ff=%d experts=%d top=%d",
               tokens, dim, ff, E, top);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "moe_experts: unknown dtype %d", dtype);
-  SLB_REQUIRE(act_kind >= kGateSilu && act_kind <= kGateClampedSwish, "moe_experts: unknown activation %d", act_kind);
+  SLB_REQUIRE(act_kind >= kGateSilu && act_kind <= kGateLast, "moe_experts: unknown activation %d", act_kind);
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const GateAct gate{act_kind, act_limit, act_alpha};

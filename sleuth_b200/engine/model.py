@@ -47,9 +47,16 @@ class Model:
             self.entry_owner.setdefault(e.cache, i)
         self.cache_requests = [self.layers[spec.schedule[self.entry_owner[c]].layer].cache_request()
                                for c in range(len(self.entry_owner))]
+        # an embedding that keeps something per sequence (the previous token, say) gets a cache entry behind the layers'
+        self.embedding_entry = None
+        request = getattr(self.embedding, "cache_request", lambda: None)()
+        if request is not None:
+            self.embedding_entry = len(self.cache_requests)
+            self.cache_requests.append(request)
+        self.pass_mix = None            # the product W [x; x0] of schedule entries that mix the embedding into the stream
         self._programs: dict = {}       # per cache: the runs of the schedule prepared for the persistent kernel
         self.pass_rows = None           # [rows, hidden] float32: vectors that schedule entries add to the stream
-        self.keeps_embedding = any(e.add_embedding for e in spec.schedule)
+        self.keeps_embedding = any(e.add_embedding or e.mix_embedding for e in spec.schedule)
         self.observe = None             # callable(schedule index, stream) after every layer application, for inspection
 
     # ---- weights ----
@@ -84,6 +91,8 @@ class Model:
             out[name] = hd[local]
         if self.spec.pass_rows:
             out[self.spec.pass_rows] = ParamDecl((self.spec.pass_rows_count, self.hidden), "vector")
+        if self.spec.pass_mix:
+            out[self.spec.pass_mix] = ParamDecl((self.hidden, 2 * self.hidden))
         return out
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -94,6 +103,9 @@ class Model:
         self.head.bind(head, embedding_table=getattr(self.embedding, "table", None))
         if self.spec.pass_rows:
             self.pass_rows = tensors[self.spec.pass_rows].to(torch.float32).contiguous()
+        if self.spec.pass_mix:
+            from ..parts.linear import Linear
+            self.pass_mix = Linear(tensors[self.spec.pass_mix], self.ctx.dtype)
 
     # ---- one step ----
     def forward(self, b, cache, ws, logits: torch.Tensor) -> torch.Tensor:
@@ -101,7 +113,10 @@ class Model:
         b.stream = torch.cuda.current_stream().cuda_stream   # inside a graph capture this is the capture stream
         mark = ws.mark()
         x = ws.take((b.T, self.hidden), torch.float32)
-        self.embedding.forward(b, x)
+        if self.embedding_entry is not None:
+            self.embedding.forward(b, x, cache.view(self.embedding_entry, writes=True))
+        else:
+            self.embedding.forward(b, x)
         x0 = None
         if self.keeps_embedding:        # some application adds the embedding's output again: keep a copy
             x0 = ws.take((b.T, self.hidden), torch.float32)
@@ -114,6 +129,13 @@ class Model:
                 i = self._run_fused(fused[i], x, b, ws)
                 continue
             e = schedule[i]
+            if e.mix_embedding:          # x <- W [x; x0]
+                from ..kernels import ops
+                m = ws.mark()
+                both = ws.take((b.T, 2 * self.hidden), self.ctx.dtype)
+                ops.stream_pair(x, x0, both, b.stream)
+                self.pass_mix.forward(both, out=x, ws=ws, stream=b.stream)
+                ws.release(m)
             if e.add_embedding or e.add_row >= 0:
                 from ..kernels import ops
                 ops.stream_inject(x, x0 if e.add_embedding else None,
@@ -193,7 +215,10 @@ class Model:
         a norm), looked for in the end parts and in each layer's ``children``."""
         parts = [self.embedding, self.head]
         for layer in self.layers:
+            parts.append(layer)           # what the arrangement itself holds (a gate's matrix)
             parts.extend(getattr(layer, "children", {}).values())
+        if self.pass_mix is not None:
+            yield self.pass_mix.weight
         from ..parts.base import Part
         while parts:
             part = parts.pop()

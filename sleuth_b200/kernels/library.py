@@ -155,11 +155,17 @@ _SIGNATURES = {
     "slb_softcap": [P, L, I, I, F, P],
     "slb_qkv_post_span": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_stream_inject": [P, P, P, I, I, P],
-    "slb_latent_post": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P],
+    "slb_pair_embed": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, L, L, P],
+    "slb_gated_norm_add": [P, P, P, L, P, P, I, I, F, P],
+    "slb_stream_pair": [P, P, P, I, I, I, P],
+    "slb_scale": [P, L, I, I, F, P, P],
+    "slb_mingru": [P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "slb_latent_post": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P],
+    "slb_latent_head_gate": [P, P, L, P, I, I, I, I, P],
     "slb_head_prompt_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "slb_latent_attention": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_latent_gate": [P, P, P, I, I, I, I, P],
-    "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
+    "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_moe_experts_tc": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, P, P],
     "slb_gemm_skinny_gated": [P, P, P, I, I, I, I, I, F, F, P, L, P, I, P],
     "slb_gemm_tc_gated": [P, P, P, I, I, I, I, I, F, F, P, P],

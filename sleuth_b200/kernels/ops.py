@@ -18,8 +18,8 @@ import torch
 from . import library
 
 DT = {torch.float32: 0, torch.bfloat16: 1}
-ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_swish": 2}
-ROUTE_SCORINGS = {"softmax_top": 0, "sigmoid": 1}
+ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_swish": 2, "gelu_tanh": 3}
+ROUTE_SCORINGS = {"softmax_top": 0, "sigmoid": 1, "softmax": 2}
 
 
 def lib() -> library.KernelLibrary:
@@ -90,8 +90,8 @@ def swiglu(gu: torch.Tensor, act: torch.Tensor, stream=None) -> None:
 
 def gated_act(gu: torch.Tensor, act: torch.Tensor, kind: str = "silu", stream=None, limit: float = 0.0,
               alpha: float = 1.0) -> None:
-    """act[t, j] = f(gu[t, j], gu[t, inter + j]): silu(g) u, relu(g) u, or the clamped swish
-    min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1)."""
+    """act[t, j] = f(gu[t, j], gu[t, inter + j]): silu(g) u, relu(g) u, the clamped swish
+    min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1), or the tanh form of gelu(g) u."""
     _cuda(gu, act)
     T, inter = act.shape
     _need(kind in ACTIVATIONS, f"gated_act: activation {kind!r} is not one of {sorted(ACTIVATIONS)}")
@@ -135,6 +135,80 @@ def stream_inject(x: torch.Tensor, again: torch.Tensor | None, row: torch.Tensor
     _need(again is None or (again.dtype == torch.float32 and again.shape == x.shape), "stream_inject: the added rows")
     _need(row is None or (row.dtype == torch.float32 and row.numel() == d), "stream_inject: the added vector")
     lib().call("slb_stream_inject", _p(x), _p(again), _p(row), T, d, stream if stream is not None else current_stream())
+
+
+def pair_embed(ids, ids_map, pairs, x, tok_seq, tok_pos, seq_start, slots, last, vocab: int, buckets: int, mul_prev: int,
+               mul_cur: int, stream=None) -> None:
+    """x[t] += pairs[(previous token * mul_prev + token * mul_cur) mod buckets], or pairs[buckets] for a sequence's first
+    token. ``pairs`` [buckets + 1, dim]; ``last`` int32 [slots]: every sequence's last token so far, read for the first
+    token of a step and left for the next step."""
+    _cuda(ids, ids_map, pairs, x, tok_seq, tok_pos, seq_start, slots, last)
+    T, d = x.shape
+    _need(x.dtype == torch.float32 and pairs.dtype in DT and tuple(pairs.shape) == (buckets + 1, d), "pair_embed: table or stream")
+    _need(last.dtype == torch.int32 and last.dim() >= 1 and ids.dtype == torch.int32, "pair_embed: int32 ids and state")
+    _need(ids_map is not None or ids.numel() >= T, "pair_embed: one id per row of x")
+    for t in (tok_seq, tok_pos, seq_start, slots):
+        _need(t.dtype == torch.int32, "pair_embed: the batch tables are int32")
+    lib().call("slb_pair_embed", _p(ids), _p(ids_map), _p(pairs), DT[pairs.dtype], _p(x), _p(tok_seq), _p(tok_pos), _p(seq_start),
+               _p(slots), _p(last), T, d, int(vocab), int(buckets), int(mul_prev), int(mul_cur),
+               stream if stream is not None else current_stream())
+
+
+def gated_norm_add(x, y, g, bias, gain, eps: float, stream=None) -> None:
+    """x += rmsnorm(y * sigmoid(g + bias)) * gain, row by row in float32; without ``g``: x += rmsnorm(y) * gain. ``y`` is
+    overwritten. ``g`` may be a view of a wider float32 matrix (unit column stride)."""
+    _cuda(x, y, bias, gain)
+    T, d = x.shape
+    _need(x.dtype == torch.float32 and y.dtype == torch.float32 and y.shape == x.shape, "gated_norm_add: the stream and the sublayer's result are float32")
+    _need(gain.dtype == torch.float32 and gain.numel() == d, "gated_norm_add: gain")
+    stride = 0
+    if g is not None:
+        _need(g.is_cuda and g.dtype == torch.float32 and g.dim() == 2 and g.shape == x.shape and g.stride(1) == 1,
+              "gated_norm_add: the gate's values are float32, one per element")
+        stride = g.stride(0) if T > 1 else d
+        _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == d), "gated_norm_add: bias")
+    lib().call("slb_gated_norm_add", _p(x), _p(y), _p(g), stride, _p(bias) if g is not None else None, _p(gain), T, d, float(eps),
+               stream if stream is not None else current_stream())
+
+
+def stream_pair(a, b, out, stream=None) -> None:
+    """out[t] = [a[t] | b[t]]: two float32 streams side by side in ``out``'s dtype."""
+    _cuda(a, b, out)
+    T, d = a.shape
+    _need(a.dtype == torch.float32 and b.dtype == torch.float32 and b.shape == a.shape and out.shape == (T, 2 * d)
+          and out.dtype in DT, "stream_pair: shapes or dtypes")
+    lib().call("slb_stream_pair", _p(a), _p(b), _p(out), DT[out.dtype], T, d, stream if stream is not None else current_stream())
+
+
+def scale(v: torch.Tensor, factor: float, stream=None, add: torch.Tensor | None = None) -> None:
+    """v <- v * factor (+ add[column]) in place; v float32 [rows, cols] with unit column stride."""
+    _need(v.is_cuda and v.dtype == torch.float32 and v.dim() == 2 and v.stride(1) == 1, "scale: a float32 matrix")
+    _need(add is None or (add.is_cuda and add.dtype == torch.float32 and add.numel() == v.shape[1]), "scale: the added row")
+    lib().call("slb_scale", _p(v), v.stride(0) if v.shape[0] > 1 else v.shape[1], v.shape[0], v.shape[1], float(factor), _p(add),
+               stream if stream is not None else current_stream())
+
+
+def mingru_scratch_floats(n_seqs: int, max_count: int, width: int) -> int:
+    fn = lib().dll.slb_mingru_scratch_floats
+    fn.argtypes, fn.restype = [ctypes.c_int] * 3, ctypes.c_longlong
+    return int(fn(int(n_seqs), int(max_count), int(width)))
+
+
+def mingru(p, bz, bu, state, slots, seq_start, y, max_count: int, scratch=None, stream=None) -> None:
+    """The minGRU recurrence over each sequence's tokens of the step. p [T, 3 * W] float32: the stacked projections
+    [z | u | g]; z = sigmoid(z + bz), u = u + bu, c = u + 1/2 where u >= 0 else sigmoid(u);
+    S <- (1 - z) S + z c from state[slot]; y[t] = S * silu(g). ``state`` float32 [slots, W] is updated."""
+    _cuda(p, bz, bu, state, slots, seq_start, y, scratch)
+    T, W = y.shape
+    n = slots.numel()
+    _need(p.dtype == torch.float32 and p.shape == (T, 3 * W), "mingru: the projections are float32 [tokens, 3 * width]")
+    _need(bz.dtype == torch.float32 and bu.dtype == torch.float32 and bz.numel() == W and bu.numel() == W, "mingru: biases")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == W and y.dtype in DT, "mingru: state or output")
+    _need(slots.dtype == torch.int32 and seq_start.dtype == torch.int32 and seq_start.numel() >= n + 1, "mingru: batch tables")
+    need = mingru_scratch_floats(n, max_count, W)
+    _need(need == 0 or (scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need), "mingru: scratch")
+    lib().call("slb_mingru", _p(p), _p(bz), _p(bu), _p(state), _p(slots), _p(seq_start), _p(y), _p(scratch), n, int(max_count), W,
+               DT[y.dtype], stream if stream is not None else current_stream())
 
 
 def qkv_post(qkv, bias, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table,
@@ -761,34 +835,38 @@ def sample(logits: torch.Tensor, limit: int, temperature: float, top_k: int, top
 
 # ---- attention through low-rank latents (csrc/latent_attention.cu) ----
 def latent_post(lat, q_gain, c_gain, cos, sin, cq, pool, tok_seq, tok_pos, block_table, q_rank: int, rank: int,
-                rot_dim: int, rotated: int, eps: float, stream=None, c_out=None, k_out=None) -> None:
+                rot_dim: int, rotated: int, eps: float, stream=None, c_out=None, k_out=None, dtype=None) -> None:
     """lat [T, q_rank + rank + rot_dim] float32 (the two down-projections' output): the normed query latent goes to
     ``cq`` [T, q_rank]; the normed latent and the rotated key part go to the token's row of ``pool``
     [pages, 64, rank + rot_dim] (``pool`` None: nothing is stored). ``rotated``: how many leading channels of the key
     part turn. ``c_out`` [T, rank] and ``k_out`` [T, rot_dim]: the same latent and key part once more, side by side in
-    the order of the step's tokens (for a step that multiplies its own tokens' latents)."""
+    the order of the step's tokens (for a step that multiplies its own tokens' latents). ``lat`` may have more columns
+    than the three parts (they are not read). With ``q_rank`` 0 there is no query latent: ``q_gain`` and ``cq`` are None
+    and ``dtype`` names the dtype of what is stored."""
     _cuda(lat, q_gain, c_gain, cos, sin, cq, pool, tok_seq, tok_pos, block_table, c_out, k_out)
     _need((c_out is None) == (k_out is None), "latent_post: the two side-by-side outputs go together")
+    T = lat.shape[0]
+    dtype = cq.dtype if cq is not None else (dtype or (pool.dtype if pool is not None else c_out.dtype))
     if c_out is not None:
-        _need(c_out.shape == (cq.shape[0], rank) and k_out.shape == (cq.shape[0], rot_dim) and c_out.dtype == k_out.dtype == cq.dtype,
+        _need(c_out.shape == (T, rank) and k_out.shape == (T, rot_dim) and c_out.dtype == k_out.dtype == dtype,
               "latent_post: side-by-side outputs")
-    T = cq.shape[0]
-    _need(lat.dtype == torch.float32 and lat.shape == (T, q_rank + rank + rot_dim), "latent_post: input shape or dtype")
-    _need(cq.shape == (T, q_rank) and cq.dtype in DT, "latent_post: query latent")
-    _need(q_gain.dtype == torch.float32 and q_gain.numel() == q_rank and c_gain.dtype == torch.float32
-          and c_gain.numel() == rank, "latent_post: gains")
+    _need(lat.dtype == torch.float32 and lat.dim() == 2 and lat.shape[1] >= q_rank + rank + rot_dim, "latent_post: input shape or dtype")
+    _need(dtype in DT and (q_rank == 0) == (cq is None), "latent_post: query latent")
+    if cq is not None:
+        _need(cq.shape == (T, q_rank) and q_gain.dtype == torch.float32 and q_gain.numel() == q_rank, "latent_post: query latent and its gain")
+    _need(c_gain.dtype == torch.float32 and c_gain.numel() == rank, "latent_post: gains")
     if rotated:
         _need(cos is not None and cos.dtype == torch.float32 and cos.shape[1] == rotated // 2 and sin.shape == cos.shape,
               "latent_post: rotation tables")
     stride = 0
     if pool is not None:
-        _need(pool.dtype == cq.dtype and tuple(pool.shape[1:]) == (64, rank + rot_dim), "latent_post: pool shape or dtype")
+        _need(pool.dtype == dtype and tuple(pool.shape[1:]) == (64, rank + rot_dim), "latent_post: pool shape or dtype")
         _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "latent_post: block table")
         stride = block_table.shape[1]
     _need(tok_seq.dtype == torch.int32 and tok_pos.dtype == torch.int32, "latent_post: token tables are int32")
     lib().call("slb_latent_post", _p(lat), _p(q_gain), _p(c_gain), _p(cos), _p(sin), _p(cq), _p(pool), _p(tok_seq),
-               _p(tok_pos), _p(block_table), stride, T, q_rank, rank, rot_dim, rotated, float(eps), DT[cq.dtype],
-               _p(c_out), _p(k_out), stream if stream is not None else current_stream())
+               _p(tok_pos), _p(block_table), stride, T, q_rank, rank, rot_dim, rotated, float(eps), DT[dtype],
+               _p(c_out), _p(k_out), lat.shape[1], stream if stream is not None else current_stream())
 
 
 def latent_attention_supported(rank: int, rot_dim: int) -> bool:
@@ -878,6 +956,17 @@ def latent_gate(val, g, y, stream=None) -> None:
     lib().call("slb_latent_gate", _p(val), _p(g), _p(y), T, H, dv, DT[y.dtype], stream if stream is not None else current_stream())
 
 
+def latent_head_gate(val, g, y, stream=None) -> None:
+    """y[t, h, :] = val[h, t, :] * sigmoid(g[t, h]): one gate value per head. val [heads, T, width], y [T, heads * width];
+    g float32 [T, heads], possibly a view of a wider matrix (unit column stride)."""
+    _cuda(val, y)
+    H, T, dv = val.shape
+    _need(y.shape == (T, H * dv) and val.dtype == y.dtype and y.dtype in DT, "latent_head_gate: shapes or dtypes")
+    _need(g.is_cuda and g.dtype == torch.float32 and g.shape == (T, H) and g.stride(1) == 1, "latent_head_gate: the gates are float32 [tokens, heads]")
+    lib().call("slb_latent_head_gate", _p(val), _p(g), g.stride(0) if T > 1 else H, _p(y), T, H, dv, DT[y.dtype],
+               stream if stream is not None else current_stream())
+
+
 # ---- routed experts (csrc/moe.cu) ----
 def moe_tile_words(tokens: int, top: int, experts: int) -> int:
     """int32 words of the row-tile table that ``moe_route`` writes for ``moe_experts_tc``."""
@@ -890,22 +979,26 @@ MOE_FEW_PAIRS = 64      # up to this many (token, choice) pairs ``moe_experts`` 
 
 def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top: int, stream=None, logits=None,
               tiles=None, layout: bool = True, scoring: str = "softmax_top", groups: int = 1, keep: int = 1,
-              scale: float = 1.0, logits_ready: bool = False) -> None:
+              scale: float = 1.0, logits_ready: bool = False, pick_bias=None) -> None:
     """Router logits in float32, then the choice. ``scoring="softmax_top"``: the ``top`` largest logits, weights =
     softmax over those. ``scoring="sigmoid"``: scores = sigmoid(logits); the experts form ``groups`` equal groups of
     neighbours, a group scores the sum of its two largest scores, only experts of the ``keep`` best groups can be
-    chosen; the ``top`` largest scores, weights = score / (their sum + 1e-20) * ``scale``. Then the (token, choice)
+    chosen; the ``top`` largest scores, weights = score / (their sum + 1e-20) * ``scale``. ``scoring="softmax"``:
+    scores = softmax over all experts' logits; the ``top`` largest of score + ``pick_bias`` (a float32 correction per
+    expert, or None) are chosen; weights = the chosen scores * ``scale``, not renormalised. Then the (token, choice)
     pairs are laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order
     [T * top] (the pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]. ``logits``: float32
     scratch [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k
     ascending). ``logits_ready``: ``logits`` holds the router's logits already (a product formed them; no bias).
     ``layout=False`` leaves counts, place and order unwritten: ``moe_experts`` with ``choice`` does not read
     them for steps of at most ``MOE_FEW_PAIRS`` pairs."""
-    _cuda(h, w_router, bias, choice, weight, rank, counts, place, order, logits, tiles)
+    _cuda(h, w_router, bias, choice, weight, rank, counts, place, order, logits, tiles, pick_bias)
     T, d = h.shape
     E = w_router.shape[0]
     _need(h.dtype in DT and w_router.dtype == torch.float32 and w_router.shape == (E, d), "moe_route: input or router matrix")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "moe_route: bias")
+    _need(pick_bias is None or (pick_bias.dtype == torch.float32 and pick_bias.numel() == E and scoring == "softmax"),
+          "moe_route: the choice correction is float32, one per expert, and goes with the softmax scoring")
     _need(scoring in ROUTE_SCORINGS, f"moe_route: scoring {scoring!r} is not one of {sorted(ROUTE_SCORINGS)}")
     for t in (choice, rank, place, order):
         _need(t.dtype == torch.int32 and t.numel() >= T * top, "moe_route: int32 tables of tokens * top entries")
@@ -913,7 +1006,7 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
           "moe_route: weights or counts")
     _need(logits is None or (logits.dtype == torch.float32 and logits.numel() >= T * E), "moe_route: scratch for the logits")
     _need(tiles is None or (tiles.dtype == torch.int32 and tiles.numel() >= moe_tile_words(T, top, E)), "moe_route: row-tile table")
-    lib().call("slb_moe_route", _p(h), _p(w_router), _p(bias), _p(choice), _p(weight), _p(rank), _p(counts), _p(place),
+    lib().call("slb_moe_route", _p(h), _p(w_router), _p(bias), _p(pick_bias), _p(choice), _p(weight), _p(rank), _p(counts), _p(place),
                _p(order), _p(logits), _p(tiles), 1 if layout else 0, T, d, E, int(top), ROUTE_SCORINGS[scoring], int(groups),
                int(keep), float(scale), 1 if logits_ready else 0, DT[h.dtype], stream if stream is not None else current_stream())
 

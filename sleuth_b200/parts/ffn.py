@@ -1,5 +1,6 @@
 """Feed-forward parts. ``gated_mlp``: down(f(gate(h), up(h))) without biases, f = silu(g) u
-(sleuth/forge/model/mlp.py:25-41), relu(g) u or the clamped swish (product, then the gated-activation kernel). Gate and up matrices are stacked at load time into one
+(sleuth/forge/model/mlp.py:25-41), relu(g) u, the tanh form of gelu(g) u or the clamped swish (in the products' epilogues, or
+product, then the gated-activation kernel). Gate and up matrices are stacked at load time into one
 ``[2 * intermediate, hidden]`` matrix, so one product feeds the activation kernel."""
 
 from __future__ import annotations
@@ -30,7 +31,7 @@ class GatedMLP(Part):
             raise ValueError(f"gated_mlp: the clamped swish needs a positive limit, got {spec.limit}")
         self.silu = spec.activation == "silu"
         # the products' epilogues apply silu and the clamped swish themselves; relu runs as product + activation kernel
-        self.fused = spec.activation in ("silu", "clamped_swish")
+        self.fused = spec.activation in ("silu", "clamped_swish", "gelu_tanh")
         self.gate = (spec.activation, spec.limit, spec.alpha)
         self.spec, self.ctx = spec, ctx
         self.gate_up = self.down = None

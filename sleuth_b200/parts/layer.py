@@ -4,6 +4,9 @@
 (``norm2`` absent) the feed-forward reads norm1's output too; the feed-forward may be absent.
 
 ``prenorm``: x += mixer(norm1(x)); x += ffn(norm2(x)) (sleuth/forge/model/transformer.py:78,87-88,96,99).
+``sandwich``: a norm in front of and behind each sublayer, x += post1(mixer(norm1(x))), then x += post2(ffn(norm2(x)));
+with ``gated`` each sublayer's result is multiplied by sigmoid(W h + b) of the sublayer's own input h before its norm.
+
 The layer owns the residual arrangement only; the parts it is given decide everything else. The sum
 itself is a float32 accumulation into the stream, done by the last product of the mixer or ffn.
 """
@@ -15,7 +18,8 @@ import os
 import torch
 
 from ..kernels import ops
-from .base import BuildContext, Normed, Part, build_ffn, build_mixer, build_norm, lead_weight_of, register_layer
+from .base import BuildContext, Normed, ParamDecl, Part, build_ffn, build_mixer, build_norm, lead_weight_of, register_layer
+from .linear import Linear
 from .spec import LayerSpec
 
 # A parallel layer's mixer and feed-forward read the same x and need nothing from each other. In a step that brings one
@@ -157,5 +161,74 @@ class ParallelLayer(Part):
         ops.add(x, x2, stream=b.stream)
 
 
+class SandwichLayer(Part):
+    """x += post1(gate1 * mixer(norm1(x))); x += post2(gate2 * ffn(norm2(x))), gate_k = sigmoid(W_k h + b_k) of the
+    sublayer's input h (only with ``spec.gated``). A sublayer adds its result into a zeroed float32 buffer of the
+    stream's shape (its last product accumulates, as it would into the stream); one kernel then applies the gate,
+    normalises the row and adds it to the stream. The gate's pre-activations are float32. The feed-forward may be absent.
+    The closing norms must be RMS norms (their gain and eps are handed to that kernel)."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext):
+        self.ctx, self.gated = ctx, bool(spec.gated)
+        self.hidden = spec.norm1.dim
+        self.norm1 = build_norm(spec.norm1, ctx)
+        self.mixer = build_mixer(spec.mixer, ctx)
+        self.post1 = build_norm(spec.post1, ctx)
+        self.ffn = build_ffn(spec.ffn, ctx) if spec.ffn is not None else None
+        self.children = {"norm1": self.norm1, "mixer": self.mixer, "post1": self.post1}
+        if self.ffn is not None:
+            self.norm2, self.post2 = build_norm(spec.norm2, ctx), build_norm(spec.post2, ctx)
+            self.children.update({"norm2": self.norm2, "ffn": self.ffn, "post2": self.post2})
+        for name, part in self.children.items():
+            if name.startswith("post") and not getattr(part, "fusable", False):
+                raise ValueError("sandwich layer: the norm behind a sublayer must be an RMS norm")
+        self.gate1 = self.gate2 = self.bias1 = self.bias2 = None
+        self.capturable = all(getattr(p, "capturable", True) for p in self.children.values())
+
+    def declare(self):
+        out = PreNormLayer.declare(self)
+        if self.gated:
+            for k in ("1", "2") if self.ffn is not None else ("1",):
+                out[f"gate{k}.weight"] = ParamDecl((self.hidden, self.hidden))
+                out[f"gate{k}.bias"] = ParamDecl((self.hidden,), "vector")
+        return out
+
+    def bind(self, tensors):
+        PreNormLayer.bind(self, tensors)
+        if self.gated:
+            self.gate1, self.bias1 = Linear(tensors["gate1.weight"], self.ctx.dtype), tensors["gate1.bias"]
+            if self.ffn is not None:
+                self.gate2, self.bias2 = Linear(tensors["gate2.weight"], self.ctx.dtype), tensors["gate2.bias"]
+
+    cache_request = PreNormLayer.cache_request
+
+    def lead_weight(self):
+        return lead_weight_of(self.mixer)
+
+    def forward(self, x, b, view, ws):
+        after = getattr(b, "next_read", None)
+        self._sublayer(self.norm1, self.mixer, self.post1, self.gate1, self.bias1, x, b, ws, view,
+                       lead_weight_of(self.ffn) if self.ffn is not None else after)
+        if self.ffn is not None:
+            self._sublayer(self.norm2, self.ffn, self.post2, self.gate2, self.bias2, x, b, ws, None, after)
+        b.next_read = after
+
+    def _sublayer(self, norm, part, post, gate, bias, x, b, ws, view, after):
+        mark = ws.mark()
+        h = ws.take(x.shape, self.ctx.dtype)
+        norm.forward(x, h, stream=b.stream)
+        y = ws.take(x.shape, torch.float32)
+        y.zero_()
+        b.next_read = gate.weight if gate is not None else after
+        if view is not None or part is self.mixer:
+            part.forward(h, y, b, view, ws)
+        else:
+            part.forward(h, y, b, ws)
+        g = gate.forward(h, ws=ws, stream=b.stream, out_dtype=torch.float32, next_read=after) if gate is not None else None
+        ops.gated_norm_add(x, y, g, bias, post.weight, post.eps, b.stream)
+        ws.release(mark)
+
+
+register_layer("sandwich", SandwichLayer)
 register_layer("prenorm", PreNormLayer)
 register_layer("parallel", ParallelLayer)

@@ -3,7 +3,8 @@
 Router logits z = W_r h + b in float32 (W_r and b are kept in float32; h is the layer's normed input in the run
 dtype). A token uses the ``top`` experts with the largest logits, weighted by the softmax over those logits alone, or
 (``scoring="sigmoid"``) those with the largest sigmoid scores among the best groups of neighbouring experts, weighted
-by score / sum of the chosen scores, scaled; an expert is down(f(gate h, up h)) with one of the gated activations. The
+by score / sum of the chosen scores, scaled, or (``scoring="softmax"``) those with the largest softmax score plus a
+correction per expert, weighted by the uncorrected scores, scaled and not renormalised; an expert is down(f(gate h, up h)) with one of the gated activations. The
 part's output, the weighted sum (plus a shared expert that every token runs, when the spec names one), is added into
 the stream.
 
@@ -40,6 +41,8 @@ class RoutedExperts(Part):
             raise ValueError(f"routed_experts: scoring {spec.scoring!r} is not one of {sorted(ops.ROUTE_SCORINGS)}")
         if spec.groups < 1 or spec.experts % spec.groups or not 1 <= spec.keep_groups <= spec.groups:
             raise ValueError(f"routed_experts: {spec.experts} experts in {spec.groups} groups of which {spec.keep_groups} are kept")
+        if spec.choice_bias and spec.scoring != "softmax":
+            raise ValueError("routed_experts: a choice correction goes with the softmax scoring over all experts")
         if spec.groups > 1 and spec.scoring != "sigmoid":
             raise ValueError("routed_experts: groups of experts go with the sigmoid scoring")
         if spec.keep_groups * (spec.experts // spec.groups) < spec.top:
@@ -47,7 +50,7 @@ class RoutedExperts(Part):
         if spec.activation == "clamped_swish" and not spec.limit > 0:
             raise ValueError(f"routed_experts: the clamped swish needs a positive limit, got {spec.limit}")
         self.spec, self.ctx = spec, ctx
-        self.w_router = self.bias = self.w_gate_up = self.w_down = self.router_product = None
+        self.w_router = self.bias = self.w_gate_up = self.w_down = self.router_product = self.pick_bias = None
         self.shared = build_ffn(spec.shared, ctx) if spec.shared is not None else None
 
     def lead_weight(self):
@@ -58,6 +61,8 @@ class RoutedExperts(Part):
         d = {"router.weight": ParamDecl((s.experts, s.hidden), "vector")}
         if s.router_bias:
             d["router.bias"] = ParamDecl((s.experts,), "vector")
+        if s.choice_bias:
+            d["correction"] = ParamDecl((s.experts,), "vector")
         for e in range(s.experts):
             d[f"e{e}.gate.weight"] = ParamDecl((s.intermediate, s.hidden))
             d[f"e{e}.up.weight"] = ParamDecl((s.intermediate, s.hidden))
@@ -71,6 +76,7 @@ class RoutedExperts(Part):
         s, dt = self.spec, self.ctx.dtype
         self.w_router = t["router.weight"].to(torch.float32).contiguous()
         self.bias = t["router.bias"].to(torch.float32).contiguous() if s.router_bias else None
+        self.pick_bias = t["correction"].to(torch.float32).contiguous() if s.choice_bias else None
         self.w_gate_up = torch.stack([torch.cat([t[f"e{e}.gate.weight"], t[f"e{e}.up.weight"]], dim=0)
                                       for e in range(s.experts)]).to(dt).contiguous()
         self.w_down = torch.stack([t[f"e{e}.down.weight"] for e in range(s.experts)]).to(dt).contiguous()
@@ -114,7 +120,7 @@ class RoutedExperts(Part):
         tiles = ws.take((ops.moe_tile_words(T, s.top, s.experts),), torch.int32) if grouped else None
         ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits, tiles,
                       layout=pairs > ops.MOE_FEW_PAIRS, scoring=s.scoring, groups=s.groups, keep=s.keep_groups,
-                      scale=s.route_scale, logits_ready=ready)
+                      scale=s.route_scale, logits_ready=ready, pick_bias=self.pick_bias)
         if grouped:
             xs = ws.take((pairs, s.hidden), dt)
             ops.moe_experts_tc(h, self.w_gate_up, self.w_down, order, place, weight, tiles, xs, act, y, x, s.top, b.stream,

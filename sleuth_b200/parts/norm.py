@@ -1,6 +1,7 @@
 """Normalisation parts. ``rmsnorm``: y = x * rsqrt(mean(x^2) + eps) * gain, float32 arithmetic on the
 float32 stream, output in the run dtype (sleuth/forge/model/norm.py:34-50). ``layernorm``: y = (x - mean) /
-sqrt(var + eps) * gain with var the mean of the squared deviations and no bias, the same way."""
+sqrt(var + eps) * gain with var the mean of the squared deviations and no bias, the same way. A norm whose spec says
+``gain="scalar"`` reads one number from the weight file and uses it for every channel."""
 
 from __future__ import annotations
 
@@ -11,18 +12,30 @@ from .base import BuildContext, ParamDecl, Part, register_norm
 from .spec import NormSpec
 
 
+def _gain_shape(spec: NormSpec) -> tuple:
+    if spec.gain not in ("vector", "scalar"):
+        raise ValueError(f"a norm's gain is 'vector' or 'scalar', not {spec.gain!r}")
+    return () if spec.gain == "scalar" else (spec.dim,)
+
+
+def _gain_vector(t: torch.Tensor, dim: int) -> torch.Tensor:
+    """The gain as the kernels read it: one float32 value per channel (a scalar gain is repeated)."""
+    return t.reshape(1).expand(dim).contiguous() if t.dim() == 0 or t.numel() == 1 and dim != 1 else t
+
+
 class RMSNorm(Part):
     fusable = True      # a product kernel may apply this norm itself from ``weight`` and ``eps``
 
     def __init__(self, spec: NormSpec, ctx: BuildContext):
         self.dim, self.eps, self.dtype = spec.dim, spec.eps, ctx.dtype
+        self.gain_shape = _gain_shape(spec)
         self.weight = None
 
     def declare(self):
-        return {"weight": ParamDecl((self.dim,), "vector", init="gain")}
+        return {"weight": ParamDecl(self.gain_shape, "vector", init="gain")}
 
     def bind(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = _gain_vector(tensors["weight"], self.dim)
 
     def fused_decode(self):
         return {"gain": self.weight, "eps": self.eps} if self.weight is not None else None
@@ -40,13 +53,14 @@ class LayerNorm(Part):
 
     def __init__(self, spec: NormSpec, ctx: BuildContext):
         self.dim, self.eps, self.dtype = spec.dim, spec.eps, ctx.dtype
+        self.gain_shape = _gain_shape(spec)
         self.weight = None
 
     def declare(self):
-        return {"weight": ParamDecl((self.dim,), "vector", init="gain")}
+        return {"weight": ParamDecl(self.gain_shape, "vector", init="gain")}
 
     def bind(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = _gain_vector(tensors["weight"], self.dim)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: torch.Tensor | None = None, stream=None):
         ops.layernorm(x, self.weight, out, self.eps, rows, stream)

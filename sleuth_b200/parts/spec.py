@@ -21,10 +21,12 @@ from typing import Mapping
 @dataclass(frozen=True)
 class NormSpec:
     """``kind="rmsnorm"``: x / sqrt(mean(x^2) + eps) * gain. ``kind="layernorm"``: (x - mean) / sqrt(var + eps) * gain,
-    var the mean of the squared deviations, no bias."""
+    var the mean of the squared deviations, no bias. ``gain="scalar"``: the gain is one number for all channels (a
+    tensor without axes in the weight file)."""
     dim: int
     eps: float
     kind: str = "rmsnorm"
+    gain: str = "vector"
 
 
 @dataclass(frozen=True)
@@ -69,7 +71,10 @@ class LatentAttentionSpec:
     ``kv_rank`` values per token, from which each head's ``plain_dim`` key values and ``value_dim`` values are
     up-projected, plus one rotated key part of ``rot_dim`` values shared by all heads. The cache keeps the latent
     and the rotated part only. ``position`` rotates the ``rot_dim`` parts (its ``head_dim`` is ``rot_dim``).
-    ``output_gate``: the heads' outputs are multiplied by sigmoid(W_g h) before the output matrix."""
+    ``output_gate``: the heads' outputs are multiplied by sigmoid(W_g h) before the output matrix; ``gate_span`` says
+    whether W_g gives one value per output channel ("channel") or one per head ("head").
+    ``q_rank`` 0: the queries do not pass through a latent; q = W_q h with the tensor ``q.weight``.
+    A position part with ``pairing="neighbours"`` turns channels 2i and 2i + 1 of the rotated parts together."""
     hidden: int
     heads: int
     plain_dim: int
@@ -80,14 +85,26 @@ class LatentAttentionSpec:
     position: PositionSpec
     scale: float
     norm_eps: float = 1e-6
-    window: int = 0              # 0 = every earlier token
+    window: int = 0              # 0 = every earlier token; n = the n most recent tokens, the query's own included
     output_gate: bool = True
     kind: str = "latent_attention"
+    gate_span: str = "channel"
+
+
+@dataclass(frozen=True)
+class MinGRUSpec:
+    """A gated recurrence whose gates read the current token only, ``width`` channels wide, with a float32 state per
+    sequence: z = sigmoid(W_z h + b_z), u = W_x h + b_x, candidate c = u + 1/2 where u >= 0 and sigmoid(u) below,
+    S_t = (1 - z) S_(t-1) + z c from S = 0, output W_o (S_t * silu(W_g h))."""
+    hidden: int
+    width: int
+    kind: str = "mingru"
 
 
 @dataclass(frozen=True)
 class GatedMLPSpec:
-    """down(f(gate(x), up(x))), no biases; ``activation``: "silu" (silu(g) u), "relu" (relu(g) u) or "clamped_swish"
+    """down(f(gate(x), up(x))), no biases; ``activation``: "silu" (silu(g) u), "relu" (relu(g) u), "gelu_tanh"
+    (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u) or "clamped_swish"
     (g' = min(g, limit), u' = clamp(u, -limit, limit): g' sigmoid(alpha g') (u' + 1))."""
     hidden: int
     intermediate: int
@@ -104,6 +121,9 @@ class RoutedExpertsSpec:
     those logits alone. ``scoring="sigmoid"``: scores = sigmoid(logits); the experts form ``groups`` equal groups of
     neighbours, a group scores the sum of its two largest scores, and only experts of the ``keep_groups`` best groups
     can be chosen; the ``top`` largest scores, weights = score / (their sum + 1e-20) * ``route_scale``.
+    ``scoring="softmax"``: scores = softmax over all experts' logits; the ``top`` largest of score + correction are chosen
+    (``choice_bias``: the tensor ``correction``, one value per expert, steers the choice only); weights = the chosen
+    experts' scores * ``route_scale``, not renormalised.
     ``activation``, ``limit``, ``alpha``: as for ``GatedMLPSpec``. ``shared``: a gated feed-forward (a ``GatedMLPSpec``)
     that every token runs and whose output is added, or None."""
     hidden: int
@@ -120,13 +140,16 @@ class RoutedExpertsSpec:
     keep_groups: int = 1
     route_scale: float = 1.0
     shared: object = None
+    choice_bias: bool = False
 
 
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: an arrangement (``kind``) of a mixer, a feed-forward and their norms. ``kind="parallel"``:
     x += mixer(norm1 x) + ffn(norm2 x), both of the same x; without ``norm2`` (None) the feed-forward reads norm1's
-    output too; it may have no feed-forward (``ffn`` is None).
+    output too; it may have no feed-forward (``ffn`` is None). ``kind="sandwich"``: a norm in front of and behind each
+    sublayer, x += post1(mixer(norm1 x)), then x += post2(ffn(norm2 x)); with ``gated`` each sublayer's result is first
+    multiplied by sigmoid(W h + b) of the sublayer's own input h (tensors ``gate1.weight``, ``gate1.bias``, ``gate2...``).
 
     ``names`` maps each part-local tensor name ("norm1.weight", "mixer.q_proj.weight",
     "ffn.down.weight", ...) to its name in the weight files."""
@@ -136,6 +159,9 @@ class LayerSpec:
     norm2: NormSpec
     names: Mapping[str, str] = field(default_factory=dict)
     kind: str = "prenorm"
+    post1: NormSpec | None = None
+    post2: NormSpec | None = None
+    gated: bool = False
 
 
 @dataclass(frozen=True)
@@ -144,11 +170,14 @@ class ScheduleEntry:
     in schedule order that names an entry owns it (and writes it), later ones only read it.
 
     Right before the application the model may add to the stream: the embedding's output once more
-    (``add_embedding``) and row ``add_row`` of the model's table of pass vectors (``ModelSpec.pass_rows``)."""
+    (``add_embedding``) and row ``add_row`` of the model's table of pass vectors (``ModelSpec.pass_rows``). With
+    ``mix_embedding`` the stream is first replaced by W [x; x0], x0 being the embedding's output and W the model's
+    ``[width, 2 * width]`` matrix ``ModelSpec.pass_mix``."""
     layer: int
     cache: int
     add_embedding: bool = False
     add_row: int = -1
+    mix_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -166,6 +195,23 @@ class EmbeddingSpec:
 
 
 @dataclass(frozen=True)
+class PairEmbeddingSpec:
+    """Token rows times ``scale`` plus a row of a hashed table of token pairs: row (previous token * ``mul_prev`` + token
+    * ``mul_cur``) mod ``buckets`` of the ``[buckets + 1, dim]`` tensor ``pairs``; a sequence's first token takes the
+    last row. The previous token is kept per sequence between steps. ``names``: checkpoint names of ``weight`` and
+    ``pairs``."""
+    vocab: int
+    dim: int
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    scale: float = 1.0
+    names: Mapping[str, str] = field(default_factory=dict)
+    name: str = ""
+    kind: str = "pair_embedding"
+
+
+@dataclass(frozen=True)
 class HeadSpec:
     """Final norm and output matrix. ``tied``: the output matrix is the embedding table. ``norm_name`` and ``name``
     are the checkpoint names of the tensors ``norm.weight`` and ``weight``; more tensors of another ``kind`` are
@@ -178,6 +224,7 @@ class HeadSpec:
     name: str = "lm_head.weight"
     kind: str = "lm_head"
     softcap: float = 0.0         # c > 0: logits <- c * tanh(logits / c)
+    scale: float = 1.0           # the logits are multiplied by this
 
 
 @dataclass(frozen=True)
@@ -190,6 +237,7 @@ class ModelSpec:
     ignored_tensors: tuple = ()   # regular expressions of tensor names a checkpoint may hold and nobody reads
     pass_rows: str | None = None  # checkpoint name of a [rows, width] table whose rows schedule entries add to the stream
     pass_rows_count: int = 0
+    pass_mix: str | None = None   # checkpoint name of the [width, 2 * width] matrix of entries with ``mix_embedding``
 
     def __post_init__(self):
         seen = set()
@@ -199,14 +247,19 @@ class ModelSpec:
             seen.add(e.cache)
             if e.add_row >= 0 and not (self.pass_rows and e.add_row < self.pass_rows_count):
                 raise ValueError(f"schedule adds row {e.add_row} of a table of {self.pass_rows_count} pass vectors")
+            if e.mix_embedding and not self.pass_mix:
+                raise ValueError("a schedule entry mixes the embedding into the stream and the model names no matrix for it")
         if seen and seen != set(range(len(seen))):
             raise ValueError(f"cache entries must be numbered 0..{len(seen) - 1} without gaps, got {sorted(seen)}")
 
 
-def looped_schedule(n_layers: int, start: int, stop: int, times: int) -> tuple:
+def looped_schedule(n_layers: int, start: int, stop: int, times: int, entry: str = "add") -> tuple:
     """Layers ``start .. stop - 1`` run ``times`` times in a row with the same weights, each pass with cache entries of
-    its own; every pass begins by adding its row of the pass vectors, and every pass but the first adds the
-    embedding's output before that. The other layers run once."""
+    its own; every pass begins by adding its row of the pass vectors. Before that, with ``entry="add"`` every pass but
+    the first adds the embedding's output; with ``entry="mix"`` every pass (the first too) replaces the stream by the
+    model's mixing matrix applied to [x; embedding output]. The other layers run once."""
+    if entry not in ("add", "mix"):
+        raise ValueError(f"a loop is entered by 'add' or 'mix', not {entry!r}")
     if not (0 <= start < stop <= n_layers and times >= 1):
         raise ValueError(f"a loop over layers {start}..{stop - 1}, {times} times, does not fit {n_layers} layers")
     out, cache = [], 0
@@ -216,7 +269,8 @@ def looped_schedule(n_layers: int, start: int, stop: int, times: int) -> tuple:
     for t in range(times):
         for i in range(start, stop):
             first = i == start
-            out.append(ScheduleEntry(i, cache, add_embedding=first and t > 0, add_row=t if first else -1))
+            out.append(ScheduleEntry(i, cache, add_embedding=first and t > 0 and entry == "add", add_row=t if first else -1,
+                                     mix_embedding=first and entry == "mix"))
             cache += 1
     for i in range(stop, n_layers):
         out.append(ScheduleEntry(i, cache))

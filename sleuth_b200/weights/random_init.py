@@ -38,7 +38,7 @@ def random_tensors(spec, seed: int, dtype: torch.dtype = torch.bfloat16, std: fl
         v = rng.standard_normal(size=d.shape) * std
         if d.init == "gain":
             v = 1.0 + v
-        out[name] = torch.from_numpy(v).to(dtype)
+        out[name] = torch.from_numpy(np.asarray(v, dtype=np.float64)).to(dtype)
     return out
 
 
