@@ -290,6 +290,7 @@ __global__ void pair_embed_kernel(const int* __restrict__ ids, const int* __rest
   const TW* src = pairs + (size_t)row * dim;
   float* out = x + (size_t)t * dim;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] += to_f32(src[i]);
+  __syncthreads();      // every warp has read the sequence's previous token before thread 0 replaces it
   if (first && threadIdx.x == 0) {
     const int e = seq_start[seq + 1] - 1;
     last[slots[seq]] = min(max(ids[map ? map[e] : e], 0), vocab - 1);

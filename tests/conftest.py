@@ -74,6 +74,22 @@ def rabadra_folders(tmp_path_factory):
     return out
 
 
+@pytest.fixture(scope="session")
+def movalorn_folders(tmp_path_factory):
+    """Model folders of the tiny Movalorn configurations, float32 weights, made once per session."""
+    import torch
+
+    import tiny_movalorn
+    from sleuth_b200.weights.random_init import write_random_model
+    out = {}
+    for name, cfg in tiny_movalorn.CONFIGS.items():
+        d = tmp_path_factory.mktemp(f"movalorn_{name}")
+        write_random_model(d, cfg, seed=tiny_movalorn.SEEDS[name], dtype=torch.float32, std=tiny_movalorn.STD)
+        tiny_movalorn.sharpen(d)
+        out[name] = str(d)
+    return out
+
+
 def pytest_terminal_summary(terminalreporter):
     """The largest differences from the plain implementation that the GPU tests saw (tests/closeness.py)."""
     import closeness

@@ -121,8 +121,10 @@ def expert_choice(h, w, p, f):
     return idx, torch.gather(s, 1, idx) * f["router"].get("scale", 1.0), margin
 
 
-def routed_experts(h, w, p, f):
-    idx, wt, _ = expert_choice(h, w, p, f)
+def routed_experts(h, w, p, f, margins=None):
+    idx, wt, margin = expert_choice(h, w, p, f)
+    if margins is not None:
+        margins.append(margin)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=h.dtype)
     for e in range(f["router"]["experts"]):
         share = (wt * (idx == e)).sum(dim=-1, keepdim=True)
@@ -139,7 +141,7 @@ def sublayer(x, fn, w, p, k, eps):
     return x + rms(y, eps) * w[p + f"norm{k}b"]
 
 
-def layer(x, w, i, L, eps):
+def layer(x, w, i, L, eps, margins=None):
     p = f"l{i}."
     if L["type"] == "latent_attention":
         mix = lambda h: latent_attention(h, w, p + "mix.", L["mixer"], eps)
@@ -154,7 +156,7 @@ def layer(x, w, i, L, eps):
     if f["kind"] == "dense":
         ff = lambda h: gated_mlp(h, w, p + "mlp.", gelu_tanh)
     elif f["kind"] == "moe":
-        ff = lambda h: routed_experts(h, w, p + "mlp.", f)
+        ff = lambda h: routed_experts(h, w, p + "mlp.", f, margins)
     else:
         raise ValueError(f"layer {i}: unknown feed-forward {f['kind']!r}")
     return sublayer(x, ff, w, p, 2, eps)
@@ -174,8 +176,9 @@ def layer_runs(cfg):
     return runs
 
 
-def forward(cfg, w, tokens, work=torch.float64, keep_stream=False):
-    """Logits [tokens, vocab] of one sequence (and, if asked, the stream after every layer application)."""
+def forward(cfg, w, tokens, work=torch.float64, keep_stream=False, margins=None):
+    """Logits [tokens, vocab] of one sequence (and, if asked, the stream after every layer application). ``margins``: a
+    list that receives, for every run of a layer with experts, by how much each token's choice of experts was clear."""
     w = {k: (v.to(work) if v.is_floating_point() else v) for k, v in w.items()}
     eps = cfg["norm"]["eps"]
     ids = torch.as_tensor(tokens, dtype=torch.long)
@@ -185,7 +188,7 @@ def forward(cfg, w, tokens, work=torch.float64, keep_stream=False):
     for i, t, first in layer_runs(cfg):
         if first:
             x = torch.cat([x, x0], dim=-1) @ w["loop.in"].T + w["loop.step"][t]
-        x = layer(x, w, i, cfg["layers"][i], eps)
+        x = layer(x, w, i, cfg["layers"][i], eps, margins)
         kept.append(x)
     logits = (rms(x, eps) * w["final.norm"]) @ w["head"].T * cfg.get("logit_scale", 1.0)
     return (logits, torch.stack(kept)) if keep_stream else logits
