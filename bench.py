@@ -546,6 +546,21 @@ def rabadra_config(width, layers, heads, kv_heads, dim, rot, experts, top, ff, g
             "layers": [{"type": "attention", "mixer": mixer, "mlp": moe} for _ in range(layers)]}
 
 
+def movalorn_config(width, layers, heads, dim, rot, vdim, kv_rank, window, gru_width, experts, top, ff, shared_ff, vocab=32768) -> dict:
+    """Recurrent and attention layers in turn (the recurrent one first), the first layer's feed-forward dense, the others
+    routed with a shared expert; all layers but the first form a loop that runs once."""
+    attn = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": kv_rank, "scale": (dim + rot) ** -0.5,
+            "rot": {"base": 10000.0, "dims": rot}, "mask": {"size": window}}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 1.0}, "shared": {"ff": shared_ff}}
+    block = []
+    for i in range(layers):
+        mixer = ("latent_attention", attn) if i % 2 else ("mingru", {"width": gru_width})
+        block.append({"type": mixer[0], "mixer": mixer[1], "mlp": moe if i else {"kind": "dense", "ff": top * ff + shared_ff}})
+    return {"architecture": "Movalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "layers": block, "loop": {"start": 1, "stop": layers, "times": 1}}
+
+
 def qwen3_like(width, layers, heads, head_dim, inter, vocab=32768) -> dict:
     return dict(CONFIG, vocab_size=vocab, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads,
                 num_key_value_heads=max(1, heads // 2), head_dim=head_dim, intermediate_size=inter, tie_word_embeddings=False)
@@ -570,7 +585,22 @@ RABADRA_SIZES = {
     "w2048": (dict(width=2048, layers=6, heads=16, kv_heads=8, dim=128, rot=64, experts=32, top=4, ff=1024, groups=8, keep=4, shared_ff=1024),
               dict(width=2048, layers=6, heads=16, head_dim=128, inter=5120)),
 }
-DESIGNS = {"lezepel": (lezepel_config, DESIGN_SIZES), "rabadra": (rabadra_config, RABADRA_SIZES)}
+# Movalorn beside Lezepel, the closest existing design (attention through a latent, routed experts, a loop): equal width,
+# depth, heads, latent and experts; Movalorn's shared expert is as wide as one routed expert, half of its layers are
+# recurrent, and its attention layers see the last 1,024 tokens.
+MOVALORN_SIZES = {
+    "w1024": (dict(width=1024, layers=8, heads=16, dim=64, rot=32, vdim=64, kv_rank=256, window=1024, gru_width=1024, experts=16, top=4,
+                   ff=768, shared_ff=768),
+              dict(width=1024, layers=8, heads=16, dim=64, rot=32, vdim=64, q_rank=384, kv_rank=256, experts=16, top=4, ff=768)),
+    "w2048": (dict(width=2048, layers=6, heads=16, dim=128, rot=64, vdim=128, kv_rank=512, window=1024, gru_width=2048, experts=64, top=6,
+                   ff=1408, shared_ff=1408),
+              dict(width=2048, layers=6, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, experts=64, top=6, ff=1408)),
+}
+DESIGNS = {"lezepel": (lezepel_config, DESIGN_SIZES), "rabadra": (rabadra_config, RABADRA_SIZES),
+           "movalorn": (movalorn_config, MOVALORN_SIZES)}
+# the model each design stands beside, and how its configuration is made from the second entry of a size
+TWINS = {"lezepel": ("qwen3", lambda kw: qwen3_like(**kw)), "rabadra": ("qwen3", lambda kw: qwen3_like(**kw)),
+         "movalorn": ("lezepel", lambda kw: lezepel_config(**kw))}
 
 
 def design_point(config: dict, prompt_len: int, batches, steps: int, warmup: int) -> dict:
@@ -632,9 +662,10 @@ def design_point(config: dict, prompt_len: int, batches, steps: int, warmup: int
 
 
 def run_design(args) -> dict:
-    """``--design lezepel`` / ``--design rabadra``: that design beside the closest existing model (the Qwen3 dense
-    decoder) at equal width, depth and active feed-forward width, random weights, bfloat16: prompt and decode throughput
-    and where the time goes. The default workload of this file does not change."""
+    """``--design lezepel`` / ``--design rabadra`` / ``--design movalorn``: that design beside the closest existing model
+    (the Qwen3 dense decoder for the first two, Lezepel for Movalorn) at equal width, depth and active feed-forward width,
+    random weights, bfloat16: prompt and decode throughput and where the time goes. The default workload of this file
+    does not change."""
     out = {"design": args.design, "dtype": "bf16", "data": "synthetic", "prompt": args.design_prompt, "sizes": {}}
     make, sizes = DESIGNS[args.design]
     for name, (mine, theirs) in sizes.items():
@@ -642,7 +673,8 @@ def run_design(args) -> dict:
             continue
         out["sizes"][name] = {
             args.design: design_point(make(**mine), args.design_prompt, (1, 8), args.design_steps, max(3, args.warmup)),
-            "qwen3": design_point(qwen3_like(**theirs), args.design_prompt, (1, 8), args.design_steps, max(3, args.warmup)),
+            TWINS[args.design][0]: design_point(TWINS[args.design][1](theirs), args.design_prompt, (1, 8), args.design_steps,
+                                                max(3, args.warmup)),
         }
     return out
 
@@ -661,7 +693,7 @@ def main() -> int:
     ap.add_argument("--skip-other-configs", action="store_true",
                     help="leave out the 32-bit block and the 4B- and 8B-shaped points (a quicker run)")
     ap.add_argument("--layers5", type=int, default=0, help="layers of the 8B-shaped point (0 = all 36)")
-    ap.add_argument("--design", choices=["lezepel", "rabadra"], default=None,
+    ap.add_argument("--design", choices=["lezepel", "rabadra", "movalorn"], default=None,
                     help="instead of the default workload: this design beside the closest existing model at equal size")
     ap.add_argument("--design-size", default="all", help="one of the sizes of --design (w1024, w2048) or all")
     ap.add_argument("--design-prompt", type=int, default=2048)

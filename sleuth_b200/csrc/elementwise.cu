@@ -267,13 +267,15 @@ __global__ void stream_inject_kernel(float* __restrict__ x, const float* __restr
 
 // A hashed table of token pairs added to the embedding: x[t, :] += pairs[row(t), :] with
 // row = (previous token * mul_prev + token * mul_cur) mod buckets, and row = buckets (the table's last row) for a
-// sequence's first token. The previous token of a step's first token comes from last[slot], the sequence's state; the
+// sequence's first token. With `table` the token's own row comes in the same pass: x[t, :] = table[token, :] * scale +
+// pairs[row(t), :]. The previous token of a step's first token comes from last[slot], the sequence's state; the
 // block of that token then leaves the step's last token there for the next step (it alone reads and writes the entry).
 template <typename TW>
 __global__ void pair_embed_kernel(const int* __restrict__ ids, const int* __restrict__ map, const TW* __restrict__ pairs,
                                   float* __restrict__ x, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                   const int* __restrict__ seq_start, const int* __restrict__ slots, int* __restrict__ last,
-                                  int dim, int vocab, int buckets, long long mul_prev, long long mul_cur) {
+                                  int dim, int vocab, int buckets, long long mul_prev, long long mul_cur,
+                                  const TW* __restrict__ table, float scale) {
   pdl_enter();
   const int t = blockIdx.x;
   const int seq = tok_seq[t];
@@ -289,7 +291,12 @@ __global__ void pair_embed_kernel(const int* __restrict__ ids, const int* __rest
   }
   const TW* src = pairs + (size_t)row * dim;
   float* out = x + (size_t)t * dim;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] += to_f32(src[i]);
+  if (table) {
+    const TW* own = table + (size_t)tok * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] = fmaf(to_f32(own[i]), scale, to_f32(src[i]));
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) out[i] += to_f32(src[i]);
+  }
   __syncthreads();      // every warp has read the sequence's previous token before thread 0 replaces it
   if (first && threadIdx.x == 0) {
     const int e = seq_start[seq + 1] - 1;
@@ -299,29 +306,49 @@ __global__ void pair_embed_kernel(const int* __restrict__ ids, const int* __rest
 
 // The end of a sublayer that is gated and normalised before it joins the stream:
 //   v = y * sigmoid(g + b) (g absent: v = y);  x += v / sqrt(mean(v^2) + eps) * w
-// y [T, dim] float32 (overwritten with v), g [T, dim] float32 with row stride g_stride, b and w [dim] float32.
+// y [T, dim] float32 (rows too wide for a thread's registers are overwritten with v), g [T, dim] float32 with row stride
+// g_stride, b and w [dim] float32.
 __global__ void gated_norm_add_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ g,
                                       long long g_stride, const float* __restrict__ b, const float* __restrict__ w, int dim,
                                       float eps) {
   pdl_enter();
   __shared__ float scratch[33];
+  constexpr int kKeep = 8;      // values a thread keeps between the two passes; rows wider than that park the rest in y
   const int r = blockIdx.x;
   float* yr = y + (size_t)r * dim;
   const float* gr = g ? g + (size_t)r * g_stride : nullptr;
-  float ss = 0.0f;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+  auto gated = [&](int i) {
     float v = yr[i];
     if (gr) {
       const float z = gr[i] + (b ? b[i] : 0.0f);
       v = v * (1.0f / (1.0f + expf(-z)));
-      yr[i] = v;
     }
+    return v;
+  };
+  float keep[kKeep];
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < kKeep; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < dim) {
+      keep[k] = gated(i);
+      ss = fmaf(keep[k], keep[k], ss);
+    }
+  }
+  for (int i = threadIdx.x + kKeep * blockDim.x; i < dim; i += blockDim.x) {
+    const float v = gated(i);
+    yr[i] = v;
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
   float* xr = x + (size_t)r * dim;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) xr[i] += (yr[i] * inv) * w[i];
+#pragma unroll
+  for (int k = 0; k < kKeep; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < dim) xr[i] += (keep[k] * inv) * w[i];
+  }
+  for (int i = threadIdx.x + kKeep * blockDim.x; i < dim; i += blockDim.x) xr[i] += (yr[i] * inv) * w[i];
 }
 
 // out[t, :] = [a[t, :] | b[t, :]] in the run dtype: two float32 streams side by side as one product's input.
@@ -528,7 +555,8 @@ extern "C" int slb_stream_inject(float* x, const float* again, const float* row,
 // entry per sequence slot (the sequence's last token so far).
 extern "C" int slb_pair_embed(const int* ids, const int* map, const void* pairs, int table_dtype, float* x, const int* tok_seq,
                               const int* tok_pos, const int* seq_start, const int* slots, int* last, int tokens, int dim,
-                              int vocab, int buckets, long long mul_prev, long long mul_cur, void* stream) {
+                              int vocab, int buckets, long long mul_prev, long long mul_cur, const void* table, float scale,
+                              void* stream) {
   SLB_REQUIRE(tokens >= 0 && dim > 0 && vocab > 0 && buckets > 0, "pair_embed: tokens=%d dim=%d vocab=%d buckets=%d", tokens, dim,
               vocab, buckets);
   SLB_REQUIRE(mul_prev >= 0 && mul_cur >= 0 && mul_prev < (1LL << 31) && mul_cur < (1LL << 31), "pair_embed: multipliers %lld, %lld",
@@ -538,10 +566,10 @@ extern "C" int slb_pair_embed(const int* ids, const int* map, const void* pairs,
   const int threads = dim >= 256 ? 256 : 64;
   if (table_dtype == kF32)
     launch(pair_embed_kernel<float>, dim3(tokens), dim3(threads), 0, s, ids, map, (const float*)pairs, x, tok_seq, tok_pos, seq_start,
-           slots, last, dim, vocab, buckets, mul_prev, mul_cur);
+           slots, last, dim, vocab, buckets, mul_prev, mul_cur, (const float*)table, scale);
   else if (table_dtype == kBF16)
     launch(pair_embed_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, s, ids, map, (const __nv_bfloat16*)pairs, x, tok_seq,
-           tok_pos, seq_start, slots, last, dim, vocab, buckets, mul_prev, mul_cur);
+           tok_pos, seq_start, slots, last, dim, vocab, buckets, mul_prev, mul_cur, (const __nv_bfloat16*)table, scale);
   else
     return fail(1, "pair_embed: unknown dtype %d", table_dtype);
   return check_launch("pair_embed");

@@ -155,11 +155,11 @@ _SIGNATURES = {
     "slb_softcap": [P, L, I, I, F, P],
     "slb_qkv_post_span": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_stream_inject": [P, P, P, I, I, P],
-    "slb_pair_embed": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, L, L, P],
+    "slb_pair_embed": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, L, L, P, F, P],
     "slb_gated_norm_add": [P, P, P, L, P, P, I, I, F, P],
     "slb_stream_pair": [P, P, P, I, I, I, P],
     "slb_scale": [P, L, I, I, F, P, P],
-    "slb_mingru": [P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "slb_mingru": [P, L, P, P, P, P, P, P, P, I, I, I, I, P],
     "slb_latent_post": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P],
     "slb_latent_head_gate": [P, P, L, P, I, I, I, I, P],
     "slb_head_prompt_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],

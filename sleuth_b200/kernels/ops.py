@@ -138,24 +138,26 @@ def stream_inject(x: torch.Tensor, again: torch.Tensor | None, row: torch.Tensor
 
 
 def pair_embed(ids, ids_map, pairs, x, tok_seq, tok_pos, seq_start, slots, last, vocab: int, buckets: int, mul_prev: int,
-               mul_cur: int, stream=None) -> None:
+               mul_cur: int, stream=None, table=None, scale: float = 1.0) -> None:
     """x[t] += pairs[(previous token * mul_prev + token * mul_cur) mod buckets], or pairs[buckets] for a sequence's first
     token. ``pairs`` [buckets + 1, dim]; ``last`` int32 [slots]: every sequence's last token so far, read for the first
-    token of a step and left for the next step."""
-    _cuda(ids, ids_map, pairs, x, tok_seq, tok_pos, seq_start, slots, last)
+    token of a step and left for the next step. With ``table`` [vocab, dim] (of ``pairs``' dtype) the token's own row comes
+    in the same pass: x[t] = table[token] * scale + the pair's row."""
+    _cuda(ids, ids_map, pairs, x, tok_seq, tok_pos, seq_start, slots, last, table)
     T, d = x.shape
     _need(x.dtype == torch.float32 and pairs.dtype in DT and tuple(pairs.shape) == (buckets + 1, d), "pair_embed: table or stream")
     _need(last.dtype == torch.int32 and last.dim() >= 1 and ids.dtype == torch.int32, "pair_embed: int32 ids and state")
     _need(ids_map is not None or ids.numel() >= T, "pair_embed: one id per row of x")
+    _need(table is None or (table.dtype == pairs.dtype and tuple(table.shape) == (vocab, d)), "pair_embed: the token table")
     for t in (tok_seq, tok_pos, seq_start, slots):
         _need(t.dtype == torch.int32, "pair_embed: the batch tables are int32")
     lib().call("slb_pair_embed", _p(ids), _p(ids_map), _p(pairs), DT[pairs.dtype], _p(x), _p(tok_seq), _p(tok_pos), _p(seq_start),
-               _p(slots), _p(last), T, d, int(vocab), int(buckets), int(mul_prev), int(mul_cur),
+               _p(slots), _p(last), T, d, int(vocab), int(buckets), int(mul_prev), int(mul_cur), _p(table), float(scale),
                stream if stream is not None else current_stream())
 
 
 def gated_norm_add(x, y, g, bias, gain, eps: float, stream=None) -> None:
-    """x += rmsnorm(y * sigmoid(g + bias)) * gain, row by row in float32; without ``g``: x += rmsnorm(y) * gain. ``y`` is
+    """x += rmsnorm(y * sigmoid(g + bias)) * gain, row by row in float32; without ``g``: x += rmsnorm(y) * gain. ``y`` may be
     overwritten. ``g`` may be a view of a wider float32 matrix (unit column stride)."""
     _cuda(x, y, bias, gain)
     T, d = x.shape
@@ -198,17 +200,19 @@ def mingru(p, bz, bu, state, slots, seq_start, y, max_count: int, scratch=None, 
     """The minGRU recurrence over each sequence's tokens of the step. p [T, 3 * W] float32: the stacked projections
     [z | u | g]; z = sigmoid(z + bz), u = u + bu, c = u + 1/2 where u >= 0 else sigmoid(u);
     S <- (1 - z) S + z c from state[slot]; y[t] = S * silu(g). ``state`` float32 [slots, W] is updated."""
-    _cuda(p, bz, bu, state, slots, seq_start, y, scratch)
+    _cuda(bz, bu, state, slots, seq_start, y, scratch)
+    _need(p.is_cuda, "mingru: the projections live on the device")
     T, W = y.shape
     n = slots.numel()
-    _need(p.dtype == torch.float32 and p.shape == (T, 3 * W), "mingru: the projections are float32 [tokens, 3 * width]")
+    _need(p.dtype == torch.float32 and p.shape == (T, 3 * W) and p.stride(1) == 1,
+          "mingru: the projections are float32 [tokens, 3 * width] (possibly a view of a wider matrix)")
     _need(bz.dtype == torch.float32 and bu.dtype == torch.float32 and bz.numel() == W and bu.numel() == W, "mingru: biases")
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == W and y.dtype in DT, "mingru: state or output")
     _need(slots.dtype == torch.int32 and seq_start.dtype == torch.int32 and seq_start.numel() >= n + 1, "mingru: batch tables")
     need = mingru_scratch_floats(n, max_count, W)
     _need(need == 0 or (scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need), "mingru: scratch")
-    lib().call("slb_mingru", _p(p), _p(bz), _p(bu), _p(state), _p(slots), _p(seq_start), _p(y), _p(scratch), n, int(max_count), W,
-               DT[y.dtype], stream if stream is not None else current_stream())
+    lib().call("slb_mingru", _p(p), p.stride(0) if T > 1 else 3 * W, _p(bz), _p(bu), _p(state), _p(slots), _p(seq_start), _p(y),
+               _p(scratch), n, int(max_count), W, DT[y.dtype], stream if stream is not None else current_stream())
 
 
 def qkv_post(qkv, bias, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table,

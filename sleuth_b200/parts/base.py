@@ -80,12 +80,26 @@ class Normed:
         return self._h
 
 
+def result_target(b, x) -> dict:
+    """How a part's last product delivers into ``x``: ``{"out": x}`` (a store) when the layer announced that ``x`` holds
+    nothing yet (``b.store_first``, which this call takes down), else ``{"into": x}`` (an accumulation)."""
+    if getattr(b, "store_first", False):
+        b.store_first = False
+        return {"out": x}
+    return {"into": x}
+
+
 class Part:
     accepts_normed = False      # True: ``forward`` takes a ``Normed`` instead of the normalised tensor
     # False: ``forward`` cannot be recorded once and replayed, because it reads host-side values of the step
     # (``b.host_slots``, ``b.host_counts``), waits for the device, or launches work whose shape depends on the data
     # (routing). A model with such a part runs its single-token steps launch by launch instead of as a CUDA graph.
     capturable = True
+    # True: the part's result reaches ``x`` through ``result_target`` first, so a layer that hands it an empty buffer need
+    # not clear it. ``accepts_rider``: the part can carry extra output rows in its first float32 product (``bind`` finds
+    # them as ``rider.weight``) and leaves their [tokens, rows] float32 result in ``b.rider``.
+    stores_result = False
+    accepts_rider = False
 
     def declare(self) -> dict[str, ParamDecl]:
         return {}

@@ -63,9 +63,11 @@ class PairEmbedding(Part):
 
     def forward(self, b, x, view):
         s = self.spec
-        ops.embed(b.token_ids, self.table, x, s.scale, b.stream, b.ids_map)
+        together = self.table.dtype == self.pairs.dtype        # one pass forms the sum of the two rows
+        if not together:
+            ops.embed(b.token_ids, self.table, x, s.scale, b.stream, b.ids_map)
         ops.pair_embed(b.token_ids, b.ids_map, self.pairs, x, b.tok_seq, b.tok_pos, b.seq_start, b.slots, view.state,
-                       s.vocab, s.buckets, s.mul_prev, s.mul_cur, b.stream)
+                       s.vocab, s.buckets, s.mul_prev, s.mul_cur, b.stream, self.table if together else None, s.scale)
 
 
 class LMHead(Part):

@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import BuildContext, Normed, ParamDecl, Part, register_ffn
+from .base import BuildContext, Normed, ParamDecl, Part, register_ffn, result_target
 from . import linear
 from .linear import Linear
 from .spec import GatedMLPSpec
@@ -22,6 +22,7 @@ FUSE_NORM = False
 
 
 class GatedMLP(Part):
+    stores_result = True
     accepts_normed = True
 
     def __init__(self, spec: GatedMLPSpec, ctx: BuildContext):
@@ -77,7 +78,7 @@ class GatedMLP(Part):
         else:
             gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
             ops.gated_act(gu, act, self.spec.activation, b.stream, self.spec.limit, self.spec.alpha)
-        self.down.forward(act, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
+        self.down.forward(act, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None), **result_target(b, x))
         ws.release(mark)
 
 

@@ -41,7 +41,7 @@ import torch
 
 from ..cache.paged import LatentRequest
 from ..kernels import ops
-from .base import BuildContext, Normed, ParamDecl, Part, build_position, register_mixer
+from .base import BuildContext, Normed, ParamDecl, Part, build_position, register_mixer, result_target
 from .linear import Linear
 from .spec import LatentAttentionSpec
 
@@ -53,6 +53,9 @@ PER_HEAD_PROMPT_TOKENS = 64
 
 
 class LatentAttention(Part):
+    stores_result = True
+    accepts_rider = True        # a layer's own rows ride at the end of the stacked down-projection
+
     def __init__(self, spec: LatentAttentionSpec, ctx: BuildContext):
         if spec.rot_dim % 2:
             raise ValueError(f"rot_dim {spec.rot_dim} must be even")
@@ -103,6 +106,10 @@ class LatentAttention(Part):
         stack = ([t["dq.weight"]] if s.q_rank else []) + [self._paired_halves(t["dkv.weight"], s.kv_rank, 0, 1)]
         if self.head_gate:
             stack.append(t["g.weight"])         # a gate value per head: its few rows ride in the stacked product
+        self.rider_rows = 0
+        if t.get("rider.weight") is not None:
+            stack.append(t["rider.weight"])
+            self.rider_rows = t["rider.weight"].shape[0]
         self.down = Linear(torch.cat(stack, dim=0) if len(stack) > 1 else stack[0], dt)     # one product, float32 result
         self.gate = Linear(t["g.weight"], dt) if s.output_gate and not self.head_gate else None
         self.uq = Linear(self._paired_halves(t["uq.weight" if s.q_rank else "q.weight"], dn, dn + P, s.heads), dt)
@@ -133,7 +140,9 @@ class LatentAttention(Part):
         g = self.gate.forward(h, ws=ws, stream=b.stream) if self.gate is not None else None
         cq = ws.take((T, s.q_rank), dt) if s.q_rank else None
         if self.head_gate:
-            g = lat[:, s.q_rank + R + P:]
+            g = lat[:, s.q_rank + R + P:s.q_rank + R + P + H]
+        if self.rider_rows:
+            b.rider = lat[:, lat.shape[1] - self.rider_rows:]
         per_head = (getattr(b, "fresh", False) and b.max_count >= PER_HEAD_PROMPT_TOKENS
                     and ops.head_prompt_supported(dn, P, dv, dt))
         c_out = ws.take((T, R), dt) if per_head else None
@@ -172,7 +181,7 @@ class LatentAttention(Part):
             ops.latent_gate(val, g, y, b.stream)
         else:
             y.view(T, H, dv).copy_(val.transpose(0, 1))
-        self.o.forward(y, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
+        self.o.forward(y, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None), **result_target(b, x))
 
 
 register_mixer("latent_attention", LatentAttention)

@@ -27,6 +27,9 @@ from .spec import LayerSpec
 # a second stream beside the mixer (into a sum of its own that one kernel adds to the stream at the end), so the layer
 # takes as long as its longer branch. Recorded steps keep the fork and the join. SLEUTH_B200_BRANCH=0 turns it off.
 BRANCH = os.environ.get("SLEUTH_B200_BRANCH", "1") != "0"
+# A gated sandwich layer lets its mixer's first float32 product carry the gate's rows (``accepts_rider``).
+# SLEUTH_B200_RIDE=0 keeps the gate a product of its own.
+RIDE = os.environ.get("SLEUTH_B200_RIDE", "1") != "0"
 _SIDE: dict = {}
 
 
@@ -194,9 +197,16 @@ class SandwichLayer(Part):
         return out
 
     def bind(self, tensors):
+        # a mixer that can carry extra rows in its first float32 product takes the gate's matrix along: one product less,
+        # and the gate's pre-activations come out of the same pass over the normed rows
+        self.rides = self.gated and getattr(self.mixer, "accepts_rider", False) and RIDE
+        if self.rides:
+            tensors = dict(tensors)
+            tensors["mixer.rider.weight"] = tensors["gate1.weight"]
         PreNormLayer.bind(self, tensors)
         if self.gated:
-            self.gate1, self.bias1 = Linear(tensors["gate1.weight"], self.ctx.dtype), tensors["gate1.bias"]
+            self.gate1 = None if self.rides else Linear(tensors["gate1.weight"], self.ctx.dtype)
+            self.bias1 = tensors["gate1.bias"]
             if self.ffn is not None:
                 self.gate2, self.bias2 = Linear(tensors["gate2.weight"], self.ctx.dtype), tensors["gate2.bias"]
 
@@ -208,24 +218,34 @@ class SandwichLayer(Part):
     def forward(self, x, b, view, ws):
         after = getattr(b, "next_read", None)
         self._sublayer(self.norm1, self.mixer, self.post1, self.gate1, self.bias1, x, b, ws, view,
-                       lead_weight_of(self.ffn) if self.ffn is not None else after)
+                       lead_weight_of(self.ffn) if self.ffn is not None else after, self.rides)
         if self.ffn is not None:
-            self._sublayer(self.norm2, self.ffn, self.post2, self.gate2, self.bias2, x, b, ws, None, after)
+            self._sublayer(self.norm2, self.ffn, self.post2, self.gate2, self.bias2, x, b, ws, None, after, False)
         b.next_read = after
 
-    def _sublayer(self, norm, part, post, gate, bias, x, b, ws, view, after):
+    def _sublayer(self, norm, part, post, gate, bias, x, b, ws, view, after, rides):
         mark = ws.mark()
-        h = ws.take(x.shape, self.ctx.dtype)
-        norm.forward(x, h, stream=b.stream)
         y = ws.take(x.shape, torch.float32)
-        y.zero_()
+        n = Normed(norm, x, ws, b.stream, self.ctx.dtype)
+        # the part alone reads the normed rows when the gate rides with it: it may then normalise inside its first product
+        h = n if rides and part.accepts_normed else n.tensor()
+        if getattr(part, "stores_result", False):
+            b.store_first = True        # the part's first delivery into y is a store
+        else:
+            y.zero_()
+        b.rider = None
         b.next_read = gate.weight if gate is not None else after
-        if view is not None or part is self.mixer:
+        if part is self.mixer:
             part.forward(h, y, b, view, ws)
         else:
             part.forward(h, y, b, ws)
-        g = gate.forward(h, ws=ws, stream=b.stream, out_dtype=torch.float32, next_read=after) if gate is not None else None
-        ops.gated_norm_add(x, y, g, bias, post.weight, post.eps, b.stream)
+        if getattr(b, "store_first", False):
+            raise RuntimeError(f"{type(part).__name__} says it stores its result and did not")
+        if rides:
+            g = b.rider         # a view into the part's scratch memory: nothing takes scratch before the next kernel reads it
+        else:
+            g = gate.forward(n.tensor(), ws=ws, stream=b.stream, out_dtype=torch.float32, next_read=after) if gate is not None else None
+        ops.gated_norm_add(x, y, g, bias if g is not None else None, post.weight, post.eps, b.stream)
         ws.release(mark)
 
 

@@ -90,6 +90,11 @@ class RoutedExperts(Part):
                 and torch.equal(self.w_router.to(torch.bfloat16).to(torch.float32), self.w_router)):
             self.router_product = Linear(self.w_router.to(torch.bfloat16), dt)
 
+    @property
+    def stores_result(self):
+        """The shared expert's last product reaches ``x`` first (and may store); the chosen experts add to it."""
+        return self.shared is not None
+
     def forward(self, h, x, b, ws):
         s, dt = self.spec, self.ctx.dtype
         if isinstance(h, Normed):

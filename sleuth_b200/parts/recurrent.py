@@ -7,7 +7,8 @@
     S_t = (1 - z) S_(t-1) + z c     (S = 0 before a sequence's first token)
     output = W_o (S_t * silu(W_g h)),  added into the stream
 
-The three projections are one stacked product with a float32 result; biases, gates, the candidate, the state and
+The three projections are one stacked product with a float32 result (a layer's own rows may ride behind them, and
+the layer's norm runs in that product's prologue where the kernel can); biases, gates, the candidate, the state and
 its product with silu(g) are float32 (``csrc/recurrent.cu``), rounded once where the output projection reads them.
 The state lives in the cache's per-sequence region (``StateRequest``): zero when a slot is taken, carried from step
 to step, so prompts may arrive whole, in portions or token by token. Nothing depends on the host's view of the step,
@@ -20,12 +21,16 @@ import torch
 
 from ..cache.paged import StateRequest
 from ..kernels import ops
-from .base import BuildContext, Normed, ParamDecl, Part, register_mixer
+from .base import BuildContext, Normed, ParamDecl, Part, register_mixer, result_target
 from .linear import Linear
 from .spec import MinGRUSpec
 
 
 class MinGRU(Part):
+    accepts_normed = True       # the stacked product normalises in its prologue where its kernel can
+    stores_result = True
+    accepts_rider = True
+
     def __init__(self, spec: MinGRUSpec, ctx: BuildContext):
         if spec.width < 1 or spec.hidden < 1:
             raise ValueError(f"mingru: width {spec.width}, hidden {spec.hidden}")
@@ -40,7 +45,12 @@ class MinGRU(Part):
 
     def bind(self, t):
         dt = self.ctx.dtype
-        self.zxg = Linear(torch.cat([t["z.weight"], t["x.weight"], t["g.weight"]], dim=0), dt)
+        stack = [t["z.weight"], t["x.weight"], t["g.weight"]]
+        self.rider_rows = 0
+        if t.get("rider.weight") is not None:       # the layer's rows ride behind the three projections
+            stack.append(t["rider.weight"])
+            self.rider_rows = t["rider.weight"].shape[0]
+        self.zxg = Linear(torch.cat(stack, dim=0), dt)
         self.o = Linear(t["o.weight"], dt)
         self.bz, self.bx = t["z.bias"].contiguous(), t["x.bias"].contiguous()
 
@@ -51,16 +61,16 @@ class MinGRU(Part):
         return self.zxg.weight if self.zxg is not None else None
 
     def forward(self, h, x, b, view, ws):
-        if isinstance(h, Normed):
-            h = h.tensor()
         W, T = self.spec.width, h.shape[0]
         mark = ws.mark()
         p = self.zxg.forward(h, ws=ws, stream=b.stream, out_dtype=torch.float32, next_read=self.o.weight)
+        if self.rider_rows:
+            b.rider = p[:, 3 * W:]
         y = ws.take((T, W), self.ctx.dtype)
         need = ops.mingru_scratch_floats(b.n, b.max_count, W)
         scratch = ws.take((need,), torch.float32) if need else None
-        ops.mingru(p, self.bz, self.bx, view.state, b.slots, b.seq_start, y, b.max_count, scratch, b.stream)
-        self.o.forward(y, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
+        ops.mingru(p[:, :3 * W], self.bz, self.bx, view.state, b.slots, b.seq_start, y, b.max_count, scratch, b.stream)
+        self.o.forward(y, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None), **result_target(b, x))
         ws.release(mark)
 
 

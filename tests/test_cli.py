@@ -148,3 +148,30 @@ def test_the_commands_serve_a_rabadra_folder_too(tmp_path):
     lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
     assert [[int(t) for t in ln.split()] for ln in lines] == [rabadra_plain.greedy_generate(cfg, w, p, 6) for p in prompts]
     assert any("RabadraConfig" in ln for ln in r.stderr.splitlines())
+
+
+@pytest.mark.gpu
+def test_the_commands_serve_a_movalorn_folder_too(tmp_path):
+    """``random-model`` and ``generate`` with a Movalorn ``config.json``, through the same registry: one-number norm
+    gains, the pair table with its extra row, recurrent and attention layers, a looped schedule."""
+    import tiny_movalorn
+    from plain import movalorn_plain
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(tiny_movalorn.K))
+    folder = tmp_path / "model"
+    r = subprocess.run([sys.executable, "-m", "sleuth_b200", "random-model", str(cfg_path), str(folder), "--seed", "3",
+                        "--dtype", "fp32"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    cfg, w = plain.read_model(folder)
+    assert cfg["architecture"] == "Movalorn" and w["bigram"].shape == (98, 72) and w["l0.norm1b"].dim() == 0
+    assert w["l1.mix.z.b"].shape == (52,) and w["loop.in"].shape == (72, 144) and "l2.rg2" not in w
+    prompts = [[5, 17, 3, 250, 9], [300, 2], [77]]
+    text = "; ".join(",".join(map(str, p)) for p in prompts)
+    r = subprocess.run([sys.executable, "-m", "sleuth_b200", "generate", str(folder), "--prompt-ids", text, "--temperature", "0",
+                        "--max-new-tokens", "6", "--dtype", "fp32", "--max-seq-len", "128"],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    assert [[int(t) for t in ln.split()] for ln in lines] == [movalorn_plain.greedy_generate(cfg, w, p, 6) for p in prompts]
+    assert any("MovalornConfig" in ln for ln in r.stderr.splitlines())
