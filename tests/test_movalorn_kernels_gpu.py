@@ -68,7 +68,8 @@ def run_mingru(p_rows, w, state, slots, counts, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("W, counts", [(52, [1, 7, 64, 3]), (256, [65, 1, 200, 64, 129]), (130, [1]), (100, [640, 63, 128])])
+@pytest.mark.parametrize("W, counts", [(52, [1, 7, 64, 3]), (256, [65, 1, 200, 64, 129]), (130, [1]), (100, [640, 63, 128]),
+                                       (33, [2100, 33, 17, 16, 700]), (160, [32, 48, 31])])
 def test_the_recurrence_in_one_pass_and_in_chunks(W, counts, dtype):
     g = torch.Generator().manual_seed(W + len(counts))
     w = gru_weights(W, W, slow=2.0)                         # slow gates: the state remembers across chunks
@@ -149,7 +150,7 @@ def test_pair_table_rows_and_the_previous_token_as_state(dtype, one_pass):
 
 
 # ---- the gated, normalised residual ----
-@pytest.mark.parametrize("d", [72, 320, 1000, 4096, 6000])
+@pytest.mark.parametrize("d", [72, 75, 320, 1000, 2050, 4096, 6000])
 def test_gated_normalised_residual(d):
     o = ops()
     g = torch.Generator().manual_seed(d)
@@ -319,7 +320,7 @@ def test_whole_prompts_with_per_head_keys_keep_the_window(H, dn, P, dv, R, windo
 
 # ---- the gate per head ----
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("H, T, dv", [(5, 37, 24), (1, 1, 8), (40, 3, 80)])
+@pytest.mark.parametrize("H, T, dv", [(5, 37, 24), (1, 1, 8), (40, 3, 80), (3, 130, 12), (7, 5, 7)])
 def test_one_gate_value_per_head(H, T, dv, dtype):
     g = torch.Generator().manual_seed(H)
     val = torch.randn(H, T, dv, generator=g).to(DT[dtype])
