@@ -416,6 +416,28 @@ __global__ void stream_pair_kernel(const float* __restrict__ a, const float* __r
   }
 }
 
+// The same in pieces of four values for widths that are multiples of four.
+template <typename TO>
+__global__ void stream_pair_vec_kernel(const float4* __restrict__ a, const float4* __restrict__ b, TO* __restrict__ out, int dim4,
+                                       size_t total4) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < total4; i += step) {
+    const size_t t = i / (2 * (size_t)dim4), c = i - t * 2 * dim4;
+    const float4 v = c < (size_t)dim4 ? a[t * dim4 + c] : b[t * dim4 + c - dim4];
+    if constexpr (sizeof(TO) == 4) {
+      reinterpret_cast<float4*>(out)[i] = v;
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(out)[i] = pk;
+    }
+  }
+}
+
 // v *= factor, or with `add` [cols]: v = v * factor + add[col]; v float32 [rows, cols] with a row stride.
 __global__ void scale_kernel(float* __restrict__ v, long long row_stride, int cols, size_t total, float factor,
                              const float* __restrict__ add) {
@@ -656,6 +678,18 @@ extern "C" int slb_stream_pair(const float* a, const float* b, void* out, int ou
   SLB_REQUIRE(out_dtype == kF32 || out_dtype == kBF16, "stream_pair: unknown dtype %d", out_dtype);
   if (tokens == 0) return 0;
   const size_t total = (size_t)tokens * 2 * dim;
+  if (dim % 4 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)b % 16 == 0 && (uintptr_t)out % 16 == 0) {
+    const size_t total4 = total / 4;
+    size_t b4 = (total4 + 255) / 256;
+    if (b4 > (size_t)sm_count() * 16) b4 = (size_t)sm_count() * 16;
+    if (out_dtype == kF32)
+      launch(stream_pair_vec_kernel<float>, dim3((int)b4), dim3(256), 0, (cudaStream_t)stream, (const float4*)a, (const float4*)b,
+             (float*)out, dim / 4, total4);
+    else
+      launch(stream_pair_vec_kernel<__nv_bfloat16>, dim3((int)b4), dim3(256), 0, (cudaStream_t)stream, (const float4*)a,
+             (const float4*)b, (__nv_bfloat16*)out, dim / 4, total4);
+    return check_launch("stream_pair");
+  }
   size_t blocks = (total + 255) / 256;
   if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
   if (out_dtype == kF32)

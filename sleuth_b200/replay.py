@@ -27,7 +27,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     p.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     p.add_argument("--max-tokens", type=int, required=True,
-                   help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                   help="most tokens live requests hold at any time (padding may be left out: a page a request is added)")
     p.add_argument("--device", default="cuda:0")
     return p
 
@@ -49,8 +49,12 @@ def main(argv=None) -> int:
         return 2
     max_pos = int(read_config_json(a.model).get("max_position_embeddings", a.max_tokens))
     max_tokens = -(-a.max_tokens // 64) * 64
+    # The cache hands out pages of 64 tokens and every live request's last page may be part empty: one page more for
+    # each request that can be live at once (each holds a token at least; 256 at most) covers a count that leaves
+    # that padding out.
+    spare = 64 * min(a.max_tokens, 256)
     engine = Engine.from_pretrained(a.model, dtype=a.dtype, max_seq_len=min(max_tokens, max_pos),
-                                    max_tokens=max_tokens, device=a.device)
+                                    max_tokens=max_tokens + spare, device=a.device)
     slot_of: dict[str, int] = {}
     for line in sys.stdin:
         line = line.strip()

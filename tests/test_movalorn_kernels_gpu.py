@@ -405,10 +405,11 @@ def test_gated_products_apply_the_tanh_gelu_in_their_epilogue(T):
 def test_two_streams_side_by_side_and_scaled_rows(dtype):
     o = ops()
     g = torch.Generator().manual_seed(8)
-    a, b = torch.randn(13, 72, generator=g), torch.randn(13, 72, generator=g)
-    both = torch.empty(13, 144, dtype=DT[dtype], device=DEV)
-    o.stream_pair(a.to(DEV), b.to(DEV), both)
-    torch.testing.assert_close(both.cpu().float(), torch.cat([a, b], -1).to(DT[dtype]).float(), rtol=0, atol=0)
+    for d in (72, 75, 1030):                                   # whole pieces of four values and not
+        a, b = torch.randn(13, d, generator=g), torch.randn(13, d, generator=g)
+        both = torch.empty(13, 2 * d, dtype=DT[dtype], device=DEV)
+        o.stream_pair(a.to(DEV), b.to(DEV), both)
+        torch.testing.assert_close(both.cpu().float(), torch.cat([a, b], -1).to(DT[dtype]).float(), rtol=0, atol=0)
     v, row = torch.randn(13, 50, generator=g), torch.randn(50, generator=g)
     vd = v.clone().to(DEV)
     o.scale(vd, 0.25)
