@@ -557,7 +557,7 @@ def movalorn_config(width, layers, heads, dim, rot, vdim, kv_rank, window, gru_w
         mixer = ("latent_attention", attn) if i % 2 else ("mingru", {"width": gru_width})
         block.append({"type": mixer[0], "mixer": mixer[1], "mlp": moe if i else {"kind": "dense", "ff": top * ff + shared_ff}})
     return {"architecture": "Movalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
-            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 1009, "mul_cur": 1}},
             "layers": block, "loop": {"start": 1, "stop": layers, "times": 1}}
 
 

@@ -109,8 +109,8 @@ __global__ void __launch_bounds__(256) moe_logits_few_kernel(const T* __restrict
 //              groups can be chosen. The `top` largest scores among them; weights = score / (sum of the chosen scores
 //              + 1e-20) * scale.
 //   scoring 2: scores = softmax(logits) over all experts; the `top` largest of score + pick_bias (a correction per expert
-//              that steers the choice only; absent = 0) are chosen; weights = the chosen experts' scores * scale, not
-//              renormalised.
+//              that moves the choice and never the weights; absent = 0) are chosen; weights = the chosen experts'
+//              scores * scale as they are.
 struct RouteRule {
   int scoring, groups, keep;
   float scale;

@@ -989,7 +989,7 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
     neighbours, a group scores the sum of its two largest scores, only experts of the ``keep`` best groups can be
     chosen; the ``top`` largest scores, weights = score / (their sum + 1e-20) * ``scale``. ``scoring="softmax"``:
     scores = softmax over all experts' logits; the ``top`` largest of score + ``pick_bias`` (a float32 correction per
-    expert, or None) are chosen; weights = the chosen scores * ``scale``, not renormalised. Then the (token, choice)
+    expert, or None) are chosen; weights = the chosen scores * ``scale`` as they are. Then the (token, choice)
     pairs are laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order
     [T * top] (the pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]. ``logits``: float32
     scratch [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k

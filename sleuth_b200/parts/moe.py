@@ -4,7 +4,7 @@ Router logits z = W_r h + b in float32 (W_r and b are kept in float32; h is the 
 dtype). A token uses the ``top`` experts with the largest logits, weighted by the softmax over those logits alone, or
 (``scoring="sigmoid"``) those with the largest sigmoid scores among the best groups of neighbouring experts, weighted
 by score / sum of the chosen scores, scaled, or (``scoring="softmax"``) those with the largest softmax score plus a
-correction per expert, weighted by the uncorrected scores, scaled and not renormalised; an expert is down(f(gate h, up h)) with one of the gated activations. The
+correction per expert, weighted by the uncorrected scores times a scale, without division by their sum; an expert is down(f(gate h, up h)) with one of the gated activations. The
 part's output, the weighted sum (plus a shared expert that every token runs, when the spec names one), is added into
 the stream.
 

@@ -1,6 +1,6 @@
 """Recurrent mixers: a float32 state per sequence instead of a cache of keys and values.
 
-``mingru``: a gated recurrence whose gates read the current token only. With h the layer's normed input and
+``mingru``: a recurrence whose update gate and candidate are functions of the step's input alone (neither sees the state), so a portion's gates are one product. With h the layer's normed input and
 ``width`` channels:
 
     z = sigmoid(W_z h + b_z)        u = W_x h + b_x        c = u + 1/2 where u >= 0, sigmoid(u) below

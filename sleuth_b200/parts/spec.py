@@ -93,7 +93,7 @@ class LatentAttentionSpec:
 
 @dataclass(frozen=True)
 class MinGRUSpec:
-    """A gated recurrence whose gates read the current token only, ``width`` channels wide, with a float32 state per
+    """A recurrence whose update gate and candidate are functions of the step's input alone, ``width`` channels wide, with a float32 state per
     sequence: z = sigmoid(W_z h + b_z), u = W_x h + b_x, candidate c = u + 1/2 where u >= 0 and sigmoid(u) below,
     S_t = (1 - z) S_(t-1) + z c from S = 0, output W_o (S_t * silu(W_g h))."""
     hidden: int
@@ -122,8 +122,8 @@ class RoutedExpertsSpec:
     neighbours, a group scores the sum of its two largest scores, and only experts of the ``keep_groups`` best groups
     can be chosen; the ``top`` largest scores, weights = score / (their sum + 1e-20) * ``route_scale``.
     ``scoring="softmax"``: scores = softmax over all experts' logits; the ``top`` largest of score + correction are chosen
-    (``choice_bias``: the tensor ``correction``, one value per expert, steers the choice only); weights = the chosen
-    experts' scores * ``route_scale``, not renormalised.
+    (``choice_bias``: the tensor ``correction``, one value per expert, moves the choice and never the weights); weights = the chosen
+    experts' scores * ``route_scale`` as they are (no division by their sum).
     ``activation``, ``limit``, ``alpha``: as for ``GatedMLPSpec``. ``shared``: a gated feed-forward (a ``GatedMLPSpec``)
     that every token runs and whose output is added, or None."""
     hidden: int

@@ -4,7 +4,7 @@ Movalorn is a decoder whose embedding adds a row of a hashed table of token pair
 layers put a norm in front of and behind each sublayer and multiply the sublayer's result by a sigmoid gate formed
 from the sublayer's input; whose norms have one gain for all channels; whose mixers are either attention through a
 low-rank latent with a sliding window, a rotated key part shared by all heads and a gate per head, or a minGRU (a
-gated recurrence whose gates read the current token only); whose feed-forwards are a gated tanh-GELU layer or a
+recurrence whose update gate and candidate come from the step's input alone); whose feed-forwards are a gated tanh-GELU layer or a
 mixture of SiLU experts chosen by softmax scores plus a correction, with a shared expert; and in which a run of
 layers may be applied several times, each pass entered through a matrix that mixes the stream with the embedding.
 

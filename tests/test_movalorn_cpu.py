@@ -140,7 +140,7 @@ def test_neighbour_rotation_is_half_rotation_of_reordered_channels():
     torch.testing.assert_close(d1, d2)
 
 
-def test_the_window_sees_itself_and_the_tokens_before_it():
+def test_a_window_of_n_holds_the_query_and_the_n_minus_one_tokens_in_front():
     torch.manual_seed(1)
     q, k, v = (torch.randn(12, 2, 4, dtype=torch.float64) for _ in range(3))
     full = plain.windowed_softmax_attention(q, k, v, 0.5, 0)
