@@ -25,8 +25,8 @@ pytestmark = pytest.mark.gpu
 # (bfloat16 bound: about twice the largest difference that rows in front of a close call showed on a B200, 0.16 on logits
 # up to 7.1 in the configuration that doubles its logits.)
 TOL = {"fp32": dict(rtol=2e-4, atol=2e-4), "bf16": dict(rtol=0.0, atol=0.3)}
-NAMES = ["K", "L", "M", "N"]
-LENGTHS = {"K": [1, 7, 66, 150], "L": [3, 64, 65, 200], "M": [2, 40, 129], "N": [5, 130, 300]}
+NAMES = ["K", "L", "M", "N", "P", "Q"]
+LENGTHS = {"K": [1, 7, 66, 150], "L": [3, 64, 65, 200], "M": [2, 40, 129], "N": [5, 130, 300], "P": [1, 33, 260], "Q": [2, 67, 200]}
 
 
 def load(folder, dtype, max_tokens=2048, **kw):

@@ -2,9 +2,10 @@
 buckets and multipliers, embedding and logit scales, norm eps; attention layers with 1, 3, 5, 6 and 40 heads, key and
 value widths equal and unequal, latent ranks that the tensor-core kernel takes (multiples of 16) and ranks it does not,
 windows shorter than a page, of exactly a page, longer than a page, longer than any test sequence, and none; minGRU
-layers narrower and wider than the model; dense, routed (top 1, 2, 3, all; with and without a shared expert) and absent
+layers narrower and wider than the model; dense, routed (top 1, 2, 3, all; one expert; with and without a shared expert) and absent
 feed-forwards in different orders; the loop over the first layers three times, over two inner layers twice, over one
-layer once, and absent."""
+layer once, over four layers four times, and absent; recurrent layers only and attention layers only (windows of 1 and 2
+tokens among them)."""
 
 from __future__ import annotations
 
@@ -73,8 +74,27 @@ N = {"architecture": "Movalorn", "vocab": 640, "width": 384, "norm": {"eps": 1e-
                 layer(A, attention(6, 32, 32, 64, 96, 130, base=1000.0), dense(256))],
      "loop": {"start": 2, "stop": 3, "times": 1}}
 
-CONFIGS = {"K": K, "L": L, "M": M, "N": N}
-SEEDS = {"K": 151, "L": 252, "M": 353, "N": 454}
+# recurrent layers only (the cache holds no pages at all, only states), one of them without feed-forward, both in a loop
+# that runs twice
+P = {"architecture": "Movalorn", "vocab": 150, "width": 96, "norm": {"eps": 1e-5}, "logit_scale": 0.7,
+     "embedding": {"scale": 2.0, "bigram": {"buckets": 53, "mul_prev": 5, "mul_cur": 11}},
+     "layers": [layer(G, gru(64), dense(128)), layer(G, gru(160), None)],
+     "loop": {"start": 0, "stop": 2, "times": 2}}
+
+# attention layers only, with the smallest windows (1: a token sees itself alone; 2) beside windows of a page less one, a
+# page and one, and two pages, four of the layers in a loop of four passes; one expert of which one is chosen; pair-table
+# multipliers whose products do not fit 32 bits
+Q = {"architecture": "Movalorn", "vocab": 150, "width": 96, "norm": {"eps": 1e-5},
+     "embedding": {"scale": 1.0, "bigram": {"buckets": 200003, "mul_prev": 1000003, "mul_cur": 999983}},
+     "layers": [layer(A, attention(4, 16, 8, 16, 32, 1), moe(1, 1, 40, scale=1.5, shared=24)),
+                layer(A, attention(2, 32, 16, 24, 48, 2), None),
+                layer(A, attention(4, 16, 16, 16, 32, 65), moe(4, 2, 32, scale=1.0, shared=32)),
+                layer(A, attention(4, 16, 16, 16, 32, 63), None),
+                layer(A, attention(4, 16, 16, 16, 32, 128), None)],
+     "loop": {"start": 1, "stop": 5, "times": 4}}
+
+CONFIGS = {"K": K, "L": L, "M": M, "N": N, "P": P, "Q": Q}
+SEEDS = {"K": 151, "L": 252, "M": 353, "N": 454, "P": 555, "Q": 656}
 STD = 0.08      # wide enough that attention is far from uniform and the experts' shares differ
 
 
