@@ -17,6 +17,9 @@ Each layer application has one cache *entry*. A part asks for what its entry nee
   number of pages: a state of a megabyte per sequence beside a cache of thousands of pages stays small. The Qwen3 decoder has none; a recurrent or convolutional mixer would keep
   its state here (the reference keeps such state beside the keys and values of the same batch row,
   sleuth/formats/qwen35.py:132-145, and a per-row token history, sleuth/forge/infer/kv_cache.py:37-43).
+* ``BundleRequest(((name, request), ...))``: an entry that holds several of the above under names (a windowed key/value
+  cache beside a recurrence's state and the tails of short convolutions, say); its view is a dictionary of the parts'
+  views. A part may itself be a bundle.
 * ``None``: the entry holds nothing.
 
 The head-major page layout lets a decode block stream one (sequence, kv head) as contiguous
@@ -51,6 +54,20 @@ class LatentRequest:
 class StateRequest:
     shape: tuple
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class BundleRequest:
+    parts: tuple                # ((name, request), ...)
+
+
+def leaf_requests(r):
+    """The requests that are no bundles inside ``r``, in order."""
+    if isinstance(r, BundleRequest):
+        for _, sub in r.parts:
+            yield from leaf_requests(sub)
+    else:
+        yield r
 
 
 @dataclass
@@ -92,7 +109,19 @@ class PagedCache:
         self.device = torch.device(device)
         self.n_pages = max(1, pages_for(max_tokens))
         self.stride = max(1, pages_for(max_seq_len))
-        self.requests = list(requests)
+        self.entry_requests = list(requests)
+        # every entry is a tree of requests; its leaves are numbered in order and laid out as the entries once were
+        self.requests = []
+        self._tree = []
+
+        def number(r):
+            if isinstance(r, BundleRequest):
+                return {name: number(sub) for name, sub in r.parts}
+            self.requests.append(r)
+            return len(self.requests) - 1
+
+        for r in self.entry_requests:
+            self._tree.append(number(r))
         if max_sequences is None:
             has_state = any(isinstance(r, StateRequest) for r in self.requests)
             max_sequences = min(self.n_pages, self.DEFAULT_SEQUENCES_WITH_STATE) if has_state else self.n_pages
@@ -136,6 +165,14 @@ class PagedCache:
         return len(self.group_requests)
 
     def view(self, entry: int, writes: bool):
+        """What the entry's owner (``writes``) or a reader gets: a view, or for a bundle a dictionary of views."""
+        def build(node):
+            if isinstance(node, dict):
+                return {name: build(sub) for name, sub in node.items()}
+            return self._leaf_view(node, writes)
+        return build(self._tree[entry])
+
+    def _leaf_view(self, entry: int, writes: bool):
         r = self.requests[entry]
         if isinstance(r, KVRequest):
             g, i = self.entry_group[entry], self.entry_index[entry]

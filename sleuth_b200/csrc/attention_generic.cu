@@ -34,6 +34,14 @@ struct AttnArgs {
   float scale;
   const float* sinks;   // [H] or null: a learned score per head that joins the softmax denominator and has no value
   int value_dim;        // width of a value row and of a head's output (head_dim is the width of queries and keys)
+  // Options of other score rules (all off by default):
+  const float* slopes;  // [H] or null: the score loses slopes[h] * (query position - key position)
+  float softcap;        // c > 0: score <- c * tanh(score / c), before the distance penalty
+  int maps;             // m > 1: a head has m score maps over the same values. q is [tokens, H * m, hd] (head by head, map by
+                        // map), a key row is [m * hd] wide (map by map), out is [tokens, H * m, value_dim]; `heads` counts H * m
+  int out_f32;          // the result is stored as float32 whatever the cache's dtype
+  const float* gate;    // null, or float32 pre-activations: the result is multiplied by sigmoid(gate[t * gate_stride + h * vd + c])
+  long long gate_stride;
 };
 
 template <typename T> struct RowDot;
@@ -88,7 +96,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_generic_kernel(AttnArgs 
   const long long item = blockIdx.x;
   const int t = (int)(item / a.heads), h = (int)(item - (long long)t * a.heads);
   const int hd = a.head_dim, vd = a.value_dim;
-  const int kh = h / (a.heads / a.kv_heads);
+  const int maps = a.maps > 1 ? a.maps : 1;
+  const int map = h % maps;                                   // h counts (head, map) pairs
+  const int kh = (h / maps) / ((a.heads / maps) / a.kv_heads);
+  const int krow = maps * hd;                                 // width of a key row of the cache
+  const float slope = a.slopes ? a.slopes[h / maps] : 0.0f;
   const int pos = a.tok_pos[t];
   const int* table = a.block_table + (size_t)a.tok_seq[t] * a.table_stride;
   const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
@@ -113,7 +125,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_generic_kernel(AttnArgs 
     if (valid) {
       const int page = table[j / kPageTokens];
       row = (page * a.kv_heads + kh) * kPageTokens + (j % kPageTokens);
-      s = RowDot<T>::run(kpool + (size_t)row * hd, qs, hd) * a.scale;
+      s = RowDot<T>::run(kpool + (size_t)row * krow + map * hd, qs, hd) * a.scale;
+      if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
+      s -= slope * (float)(pos - j);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = valid ? expf(s - m_new) : 0.0f;
@@ -149,13 +163,16 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_generic_kernel(AttnArgs 
 #pragma unroll
   for (int w = 0; w < kAttnWarps; ++w) total += part_l[w] * expf(part_m[w] - top);
   if (a.sinks) total += expf(sink - top);
-  T* o = (T*)a.out + ((size_t)t * a.heads + h) * vd;
+  const size_t orow = ((size_t)t * a.heads + h) * vd;
   const float inv = 1.0f / total;
   for (int c = threadIdx.x; c < vd; c += kAttnWarps * 32) {
     float v = 0.0f;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) v += part_acc[w][c] * expf(part_m[w] - top);
-    o[c] = from_f32<T>(v * inv);
+    v *= inv;
+    if (a.gate) v *= 1.0f / (1.0f + expf(-a.gate[(size_t)t * a.gate_stride + (size_t)h * vd + c]));
+    if (a.out_f32) ((float*)a.out)[orow + c] = v;
+    else ((T*)a.out)[orow + c] = from_f32<T>(v);
   }
 }
 
@@ -197,6 +214,36 @@ extern "C" int slb_attention_generic(const void* q, const void* k_pool, const vo
   a.tok_seq = tok_seq; a.tok_pos = tok_pos; a.block_table = block_table; a.table_stride = table_stride;
   a.tokens = tokens; a.heads = heads; a.kv_heads = kv_heads; a.head_dim = head_dim; a.window = window;
   a.scale = scale; a.sinks = sinks; a.value_dim = value_dim;
+  a.slopes = nullptr; a.softcap = 0.0f; a.maps = 1; a.out_f32 = 0; a.gate = nullptr; a.gate_stride = 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kF32) return launch_attn_generic<float>(a, s);
+  if (dtype == kBF16) return launch_attn_generic<__nv_bfloat16>(a, s);
+  return fail(1, "attention: unknown dtype %d", dtype);
+}
+
+// The same kernel with other score rules: a distance penalty per head (`slopes`), a soft cap, several score maps a head
+// over the same values (`maps`; `heads` counts heads, not maps), a float32 result, and a sigmoid gate on the result.
+extern "C" int slb_attention_scored(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                    const int* tok_seq, const int* tok_pos, const int* block_table,
+                                    int table_stride, int tokens, int heads, int kv_heads, int head_dim, int window,
+                                    float scale, const float* slopes, float softcap, int maps, int out_f32,
+                                    const float* gate, long long gate_stride, int value_dim, int dtype, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+              "attention: tokens=%d heads=%d kv_heads=%d", tokens, heads, kv_heads);
+  SLB_REQUIRE(head_dim > 0 && head_dim <= 256 && head_dim % 2 == 0,
+              "attention: head_dim %d is not supported (even, at most 256)", head_dim);
+  SLB_REQUIRE(window >= 0 && table_stride > 0, "attention: window=%d table_stride=%d", window, table_stride);
+  SLB_REQUIRE(maps >= 1 && maps <= 8 && softcap >= 0.0f, "attention: maps=%d softcap=%g", maps, (double)softcap);
+  SLB_REQUIRE(gate == nullptr || gate_stride >= (long long)heads * maps * value_dim, "attention: gate rows are too short");
+  if (value_dim == 0) value_dim = head_dim;
+  SLB_REQUIRE(value_dim > 0 && value_dim <= 256, "attention: value size %d is not supported (at most 256)", value_dim);
+  if (tokens == 0) return 0;
+  AttnArgs a;
+  a.q = q; a.k_pool = k_pool; a.v_pool = v_pool; a.out = out;
+  a.tok_seq = tok_seq; a.tok_pos = tok_pos; a.block_table = block_table; a.table_stride = table_stride;
+  a.tokens = tokens; a.heads = heads * maps; a.kv_heads = kv_heads; a.head_dim = head_dim; a.window = window;
+  a.scale = scale; a.sinks = nullptr; a.value_dim = value_dim;
+  a.slopes = slopes; a.softcap = softcap; a.maps = maps; a.out_f32 = out_f32; a.gate = gate; a.gate_stride = gate_stride;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kF32) return launch_attn_generic<float>(a, s);
   if (dtype == kBF16) return launch_attn_generic<__nv_bfloat16>(a, s);

@@ -111,6 +111,7 @@ __global__ void __launch_bounds__(256) moe_logits_few_kernel(const T* __restrict
 //   scoring 2: scores = softmax(logits) over all experts; the `top` largest of score + pick_bias (a correction per expert
 //              that moves the choice and never the weights; absent = 0) are chosen; weights = the chosen experts'
 //              scores * scale as they are.
+//   scoring 3: the scores and the choice of scoring 2; weights = score / (sum of the chosen scores + 1e-20) * scale.
 struct RouteRule {
   int scoring, groups, keep;
   float scale;
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
     __syncwarp();
   }
   float* sel = z;                      // what the choice looks at
-  if (rule.scoring == 2) {
+  if (rule.scoring >= 2) {             // 2 and 3: softmax over all experts (3 divides the chosen scores by their sum)
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
     mx = warp_max(mx);
@@ -225,7 +226,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
     }
     best_e = min(best_e, E - 1);                 // only logits that are not numbers get here
     if (k == 0) first = best;
-    const float p = rule.scoring == 2 ? z[best_e] * rule.scale : (rule.scoring == 1 ? best : expf(best - first));
+    const float p = rule.scoring == 2 ? z[best_e] * rule.scale
+                                      : (rule.scoring == 3 ? z[best_e] : (rule.scoring == 1 ? best : expf(best - first)));
     mass += p;
     __syncwarp();
     if (lane == 0) {
@@ -236,7 +238,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
     __syncwarp();
   }
   if (rule.scoring == 2) return;
-  if (rule.scoring == 1) {
+  if (rule.scoring == 1 || rule.scoring == 3) {
     for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] = weight[(size_t)t * top + k] / (mass + 1e-20f) * rule.scale;
   } else {
     for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] /= mass;
@@ -703,8 +705,8 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
               tokens, dim, E, top);
   SLB_REQUIRE(E <= 4096, "moe_route: at most 4096 experts, got %d", E);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "moe_route: unknown dtype %d", dtype);
-  SLB_REQUIRE(scoring >= 0 && scoring <= 2, "moe_route: unknown scoring %d", scoring);
-  SLB_REQUIRE(pick_bias == nullptr || scoring == 2, "moe_route: a choice correction goes with the softmax scoring over all experts");
+  SLB_REQUIRE(scoring >= 0 && scoring <= 3, "moe_route: unknown scoring %d", scoring);
+  SLB_REQUIRE(pick_bias == nullptr || scoring >= 2, "moe_route: a choice correction goes with the softmax scoring over all experts");
   if (groups <= 0) groups = 1;
   if (keep <= 0 || keep > groups) keep = groups;
   SLB_REQUIRE(E % groups == 0, "moe_route: %d experts do not form %d equal groups", E, groups);
@@ -714,7 +716,7 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
   cudaStream_t s = (cudaStream_t)stream;
   (void)rank;      // kept in the signature: callers hand over a table that older versions filled
   const RouteRule rule{scoring, groups, keep, route_scale};
-  const size_t smem = (size_t)(E + 2 * groups + (scoring == 2 ? E : 0)) * sizeof(float);
+  const size_t smem = (size_t)(E + 2 * groups + (scoring >= 2 ? E : 0)) * sizeof(float);
   const dim3 grid(tokens);
   // from a few tokens on the logits are formed 32 tokens and 16 experts at a time, each weight read once a block
   const float* given = nullptr;

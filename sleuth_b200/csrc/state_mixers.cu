@@ -1,0 +1,273 @@
+// Mixers that carry a fixed-size state per sequence instead of a growing cache: short causal convolutions over time and
+// recurrences with a matrix state and a decay (state-space duality, gated linear attention). All arithmetic is float32;
+// the states live in the cache's per-sequence regions [slots, ...] and are indexed by the step's slots.
+//
+//   causal_conv_kernel      y_t[c] = sum_j w[c, j] * u_(t - taps + 1 + j)[c] (+ bias, then silu): inputs before the step's
+//                           first token come from the sequence's state (its last taps - 1 inputs), zeros at its start
+//   conv_state_kernel       the state after the step: the sequence's last taps - 1 inputs
+//   decay_scan_kernel       S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head; a_t one factor per key channel
+//                           or one per head; v may carry a factor per (token, head)
+//   step_decay_kernel       dt = softplus(raw + bias_h), a = exp(-exp(A_log_h) * dt)   (state-space step sizes and decays)
+//   channel_decay_kernel    a = sigmoid(z + bias)^(1 / tau) = exp(-softplus(-(z + bias)) / tau)
+//   gated_group_norm_kernel rows cut into equal groups, each divided by its root mean square, times a gain, with a
+//                           silu gate in front of or behind the norm and an optional skip term D_h * x
+#include <math.h>
+
+#include "common.cuh"
+
+namespace slb {
+
+constexpr int kMaxTaps = 16;
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+// One thread per (token, channel). in: [tokens, in_stride] float32, state: [slots, taps - 1, C] (oldest first).
+__global__ void __launch_bounds__(256) causal_conv_kernel(const float* __restrict__ in, long long in_stride,
+                                                          const float* __restrict__ w, const float* __restrict__ bias,
+                                                          const float* __restrict__ state, const int* __restrict__ slots,
+                                                          const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                                                          float* __restrict__ out, long long out_stride, int tokens, int C,
+                                                          int taps, int act) {
+  pdl_enter();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * C) return;
+  const int t = (int)(i / C), c = (int)(i - (long long)t * C);
+  const int seq = tok_seq[t];
+  const int at = t - seq_start[seq];                 // index of the token within its sequence's share of the step
+  const float* st = state + ((size_t)slots[seq] * (taps - 1)) * C + c;
+  float acc = bias ? bias[c] : 0.0f;
+  for (int j = 0; j < taps; ++j) {
+    const int src = at - (taps - 1) + j;
+    const float u = src >= 0 ? in[(size_t)(t - (taps - 1) + j) * in_stride + c] : st[(size_t)(taps - 1 + src) * C];
+    acc = fmaf(w[(size_t)c * taps + j], u, acc);
+  }
+  out[(size_t)t * out_stride + c] = act ? silu_f(acc) : acc;
+}
+
+// One thread per (sequence, channel): the last taps - 1 inputs of the sequence, old ones kept where the step was short.
+__global__ void __launch_bounds__(256) conv_state_kernel(const float* __restrict__ in, long long in_stride,
+                                                         float* __restrict__ state, const int* __restrict__ slots,
+                                                         const int* __restrict__ seq_start, int n_seqs, int C, int taps) {
+  pdl_enter();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n_seqs * C) return;
+  const int seq = (int)(i / C), c = (int)(i - (long long)seq * C);
+  const int first = seq_start[seq], count = seq_start[seq + 1] - first;
+  float* st = state + ((size_t)slots[seq] * (taps - 1)) * C + c;
+  float keep[kMaxTaps];
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) {
+    if (k < taps - 1) {
+      const int src = count - (taps - 1) + k;
+      keep[k] = src >= 0 ? in[(size_t)(first + src) * in_stride + c] : st[(size_t)(taps - 1 + src) * C];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k)
+    if (k < taps - 1) st[(size_t)k * C] = keep[k];
+}
+
+struct ScanArgs {
+  const float *q, *k, *v, *a, *vs;     // rows of tokens; vs may be null
+  long long q_stride, k_stride, v_stride, a_stride, vs_stride;
+  float* state;                        // [slots, heads, N, P]
+  const int* slots;
+  const int* seq_start;
+  float* out;                          // [tokens, heads * P]
+  int n_seqs, heads, groups, N, P;
+  int a_per_channel;                   // 1: a is [tokens, heads * N]; 0: [tokens, heads]
+  float q_scale;
+};
+
+// One thread per (sequence, head, value channel p) keeps column p of the head's state, N values, in registers and walks
+// the sequence's tokens of the step. Neighbouring threads hold neighbouring p, so state and value accesses are whole
+// lines and the key, query and decay values of a token are the same addresses for a whole warp. A token's loads do not
+// depend on the state, so the compiler keeps several tokens' loads in flight.
+template <int NB>
+__global__ void __launch_bounds__(128) decay_scan_kernel(ScanArgs a) {
+  pdl_enter();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)a.n_seqs * a.heads * a.P;
+  if (i >= total) return;
+  const int p = (int)(i % a.P);
+  const int h = (int)((i / a.P) % a.heads);
+  const int seq = (int)(i / ((long long)a.P * a.heads));
+  const int g = h / (a.heads / a.groups);
+  const int N = a.N;
+  float* st = a.state + (((size_t)a.slots[seq] * a.heads + h) * N) * a.P + p;
+  float S[NB];
+#pragma unroll
+  for (int n = 0; n < NB; ++n) S[n] = n < N ? st[(size_t)n * a.P] : 0.0f;
+  const int t0 = a.seq_start[seq], t1 = a.seq_start[seq + 1];
+  for (int t = t0; t < t1; ++t) {
+    const float* qr = a.q + (size_t)t * a.q_stride + (size_t)g * N;
+    const float* kr = a.k + (size_t)t * a.k_stride + (size_t)g * N;
+    const float* ar = a.a + (size_t)t * a.a_stride + (a.a_per_channel ? (size_t)h * N : (size_t)h);
+    float v = a.v[(size_t)t * a.v_stride + (size_t)h * a.P + p];
+    if (a.vs) v *= a.vs[(size_t)t * a.vs_stride + h];
+    const float a_head = a.a_per_channel ? 1.0f : ar[0];
+    float o = 0.0f;
+#pragma unroll
+    for (int n = 0; n < NB; ++n) {
+      if (n < N) {
+        const float an = a.a_per_channel ? ar[n] : a_head;
+        S[n] = fmaf(an, S[n], kr[n] * v);
+        o = fmaf(S[n], qr[n], o);
+      }
+    }
+    a.out[(size_t)t * ((size_t)a.heads * a.P) + (size_t)h * a.P + p] = o * a.q_scale;
+  }
+#pragma unroll
+  for (int n = 0; n < NB; ++n)
+    if (n < N) st[(size_t)n * a.P] = S[n];
+}
+
+// raw: [tokens, raw_stride] (the step sizes' pre-activations of head h at raw[t * raw_stride + h]).
+__global__ void __launch_bounds__(256) step_decay_kernel(const float* __restrict__ raw, long long raw_stride,
+                                                         const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                                         float* __restrict__ dt, float* __restrict__ decay, int tokens,
+                                                         int heads) {
+  pdl_enter();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * heads) return;
+  const int t = (int)(i / heads), h = (int)(i - (long long)t * heads);
+  const float d = softplus_f(raw[(size_t)t * raw_stride + h] + dt_bias[h]);
+  dt[i] = d;
+  decay[i] = expf(-expf(a_log[h]) * d);
+}
+
+// z: [tokens, C] float32, overwritten by the decays.
+__global__ void __launch_bounds__(256) channel_decay_kernel(float* __restrict__ z, const float* __restrict__ bias,
+                                                            long long total, int C, float inv_tau) {
+  pdl_enter();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float v = z[i] + (bias ? bias[i % C] : 0.0f);
+  z[i] = expf(-softplus_f(-v) * inv_tau);
+}
+
+struct GroupNormArgs {
+  const float* y;        // [tokens, inner] the recurrence's result
+  const float* skip;     // null, or [tokens, skip_stride]: D[h] * skip[t, c] is added first (h = c / head_width)
+  long long skip_stride;
+  const float* skip_gain;
+  int head_width;
+  const float* gate;     // [tokens, gate_stride] pre-activations of the silu gate
+  long long gate_stride;
+  const float* gain;     // [gain_len]; channel c reads gain[c % gain_len]
+  int gain_len;
+  void* out;             // [tokens, inner] in the run dtype
+  int tokens, inner, groups;
+  int gate_first;        // 1: (y * silu(gate)) is normalised; 0: the normalised row is multiplied by silu(gate)
+  float eps;
+};
+
+// One block per (token, group).
+template <typename T>
+__global__ void __launch_bounds__(128) gated_group_norm_kernel(GroupNormArgs a) {
+  pdl_enter();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x / a.groups, grp = blockIdx.x % a.groups;
+  const int width = a.inner / a.groups, c0 = grp * width;
+  const float* y = a.y + (size_t)t * a.inner;
+  const float* gate = a.gate + (size_t)t * a.gate_stride;
+  float ss = 0.0f;
+  for (int c = c0 + threadIdx.x; c < c0 + width; c += blockDim.x) {
+    float v = y[c];
+    if (a.skip) v = fmaf(a.skip_gain[c / a.head_width], a.skip[(size_t)t * a.skip_stride + c], v);
+    if (a.gate_first) v *= silu_f(gate[c]);
+    ss = fmaf(v, v, ss);
+  }
+  const float r = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + a.eps);
+  T* out = (T*)a.out + (size_t)t * a.inner;
+  for (int c = c0 + threadIdx.x; c < c0 + width; c += blockDim.x) {
+    float v = y[c];
+    if (a.skip) v = fmaf(a.skip_gain[c / a.head_width], a.skip[(size_t)t * a.skip_stride + c], v);
+    if (a.gate_first) v *= silu_f(gate[c]);
+    v = v * r * a.gain[c % a.gain_len];
+    if (!a.gate_first) v *= silu_f(gate[c]);
+    out[c] = from_f32<T>(v);
+  }
+}
+
+}  // namespace slb
+
+using namespace slb;
+
+extern "C" int slb_causal_conv(const float* in, long long in_stride, const float* w, const float* bias, float* state,
+                               const int* slots, const int* tok_seq, const int* seq_start, float* out,
+                               long long out_stride, int tokens, int n_seqs, int C, int taps, int act, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && n_seqs >= 0 && C > 0 && taps >= 1 && taps <= kMaxTaps, "causal_conv: tokens=%d channels=%d taps=%d",
+              tokens, C, taps);
+  SLB_REQUIRE(in_stride >= C && out_stride >= C, "causal_conv: rows are narrower than the channels");
+  if (tokens == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long total = (long long)tokens * C;
+  launch(causal_conv_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, in, in_stride, w, bias,
+         (const float*)state, slots, tok_seq, seq_start, out, out_stride, tokens, C, taps, act);
+  int rc = check_launch("causal_conv");
+  if (rc || taps == 1) return rc;
+  const long long st = (long long)n_seqs * C;
+  launch(conv_state_kernel, dim3((unsigned)((st + 255) / 256)), dim3(256), 0, s, in, in_stride, state, slots, seq_start,
+         n_seqs, C, taps);
+  return check_launch("conv_state");
+}
+
+extern "C" int slb_decay_scan(const float* q, long long q_stride, const float* k, long long k_stride, const float* v,
+                              long long v_stride, const float* a, long long a_stride, int a_per_channel, const float* vs,
+                              long long vs_stride, float* state, const int* slots, const int* seq_start, float* out,
+                              int n_seqs, int heads, int groups, int N, int P, float q_scale, void* stream) {
+  SLB_REQUIRE(n_seqs >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && N > 0 && N <= 256 && P > 0,
+              "decay_scan: heads=%d groups=%d state rows=%d (at most 256) columns=%d", heads, groups, N, P);
+  if (n_seqs == 0) return 0;
+  ScanArgs g{q, k, v, a, vs, q_stride, k_stride, v_stride, a_stride, vs_stride, state, slots, seq_start, out,
+             n_seqs, heads, groups, N, P, a_per_channel, q_scale};
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long total = (long long)n_seqs * heads * P;
+  const dim3 grid((unsigned)((total + 127) / 128)), block(128);
+  if (N <= 16) launch(decay_scan_kernel<16>, grid, block, 0, s, g);
+  else if (N <= 32) launch(decay_scan_kernel<32>, grid, block, 0, s, g);
+  else if (N <= 64) launch(decay_scan_kernel<64>, grid, block, 0, s, g);
+  else if (N <= 128) launch(decay_scan_kernel<128>, grid, block, 0, s, g);
+  else launch(decay_scan_kernel<256>, grid, block, 0, s, g);
+  return check_launch("decay_scan");
+}
+
+extern "C" int slb_step_decay(const float* raw, long long raw_stride, const float* dt_bias, const float* a_log, float* dt,
+                              float* decay, int tokens, int heads, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && heads > 0 && raw_stride >= heads, "step_decay: tokens=%d heads=%d", tokens, heads);
+  if (tokens == 0) return 0;
+  const long long total = (long long)tokens * heads;
+  launch(step_decay_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, raw, raw_stride,
+         dt_bias, a_log, dt, decay, tokens, heads);
+  return check_launch("step_decay");
+}
+
+extern "C" int slb_channel_decay(float* z, const float* bias, int tokens, int C, float tau, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && C > 0 && tau > 0.0f, "channel_decay: tokens=%d channels=%d tau=%g", tokens, C, (double)tau);
+  if (tokens == 0) return 0;
+  const long long total = (long long)tokens * C;
+  launch(channel_decay_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, z, bias, total, C,
+         1.0f / tau);
+  return check_launch("channel_decay");
+}
+
+extern "C" int slb_gated_group_norm(const float* y, const float* skip, long long skip_stride, const float* skip_gain,
+                                    int head_width, const float* gate, long long gate_stride, const float* gain,
+                                    int gain_len, void* out, int tokens, int inner, int groups, int gate_first, float eps,
+                                    int dtype, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && inner > 0 && groups > 0 && inner % groups == 0 && gain_len > 0 && head_width > 0,
+              "gated_group_norm: inner=%d groups=%d gain=%d", inner, groups, gain_len);
+  SLB_REQUIRE(gate != nullptr && gate_stride >= inner && (skip == nullptr || (skip_gain != nullptr && skip_stride >= inner)),
+              "gated_group_norm: gate or skip rows");
+  if (tokens == 0) return 0;
+  GroupNormArgs a{y, skip, skip_stride, skip_gain, head_width, gate, gate_stride, gain, gain_len, out, tokens, inner, groups,
+                  gate_first, eps};
+  const dim3 grid((unsigned)(tokens * groups)), block(128);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kF32) launch(gated_group_norm_kernel<float>, grid, block, 0, s, a);
+  else if (dtype == kBF16) launch(gated_group_norm_kernel<__nv_bfloat16>, grid, block, 0, s, a);
+  else return fail(1, "gated_group_norm: unknown dtype %d", dtype);
+  return check_launch("gated_group_norm");
+}

@@ -82,7 +82,8 @@ class Engine:
         folder = Path(folder)
         arch, cfg, unread = parse_config(read_config_json(folder))
         with Checkpoint(folder) as ckpt:
-            spec = arch.model_spec(cfg, tensor_names=set(ckpt.names()))
+            # name -> shape: a description may ask which tensors the files hold, and read a size that only a shape gives
+            spec = arch.model_spec(cfg, tensor_names={n: tuple(ckpt.describe(n)[1]) for n in ckpt.names()})
             max_seq_len = max(1, min(int(max_seq_len), spec.max_positions))
             ctx = BuildContext(device=device, dtype=run_dtype, max_positions=-(-max_seq_len // 64) * 64)
             model = Model(spec, ctx)

@@ -110,6 +110,7 @@ class Model:
     # ---- one step ----
     def forward(self, b, cache, ws, logits: torch.Tensor) -> torch.Tensor:
         """Run the tokens of batch ``b``; fill ``logits`` [len(b.rows), vocab] (float32)."""
+        from ..kernels import ops
         b.stream = torch.cuda.current_stream().cuda_stream   # inside a graph capture this is the capture stream
         mark = ws.mark()
         x = ws.take((b.T, self.hidden), torch.float32)
@@ -117,6 +118,11 @@ class Model:
             self.embedding.forward(b, x, cache.view(self.embedding_entry, writes=True))
         else:
             self.embedding.forward(b, x)
+        xs = None
+        if self.spec.streams > 1:           # several copies of the stream: all start as the embedding's output
+            from ..kernels import ops
+            xs = ws.take((b.T, self.spec.streams * self.hidden), torch.float32)
+            ops.streams_fill(x, xs, self.spec.streams, b.stream)
         x0 = None
         if self.keeps_embedding:        # some application adds the embedding's output again: keep a copy
             x0 = ws.take((b.T, self.hidden), torch.float32)
@@ -141,13 +147,20 @@ class Model:
                 ops.stream_inject(x, x0 if e.add_embedding else None,
                                   self.pass_rows[e.add_row] if e.add_row >= 0 else None, b.stream)
             view = cache.view(e.cache, writes=self.entry_owner[e.cache] == i)
+            if e.borrow >= 0:               # the application also reads what an earlier one wrote
+                view = dict(view) if isinstance(view, dict) else {"own": view}
+                view["borrowed"] = cache.view(e.borrow, writes=False)
             following = self.layers[schedule[i + 1].layer] if i + 1 < len(schedule) and (i + 1) not in fused else None
             b.next_read = lead_weight_of(following)
-            self.layers[e.layer].forward(x, b, view, ws)
+            self.layers[e.layer].forward(x if xs is None else xs, b, view, ws)
             if self.observe is not None:
+                if xs is not None:
+                    ops.streams_sum(xs, x, b.stream)
                 self.observe(i, x)
             i += 1
         b.next_read = None
+        if xs is not None:                  # the copies' sum enters the final norm
+            ops.streams_sum(xs, x, b.stream)
         if logits.shape[0]:
             self.head.forward(x, b, logits, ws)
         ws.release(mark)

@@ -19,7 +19,7 @@ from . import library
 
 DT = {torch.float32: 0, torch.bfloat16: 1}
 ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_swish": 2, "gelu_tanh": 3}
-ROUTE_SCORINGS = {"softmax_top": 0, "sigmoid": 1, "softmax": 2}
+ROUTE_SCORINGS = {"softmax_top": 0, "sigmoid": 1, "softmax": 2, "softmax_norm": 3}
 
 
 def lib() -> library.KernelLibrary:
@@ -989,7 +989,8 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
     neighbours, a group scores the sum of its two largest scores, only experts of the ``keep`` best groups can be
     chosen; the ``top`` largest scores, weights = score / (their sum + 1e-20) * ``scale``. ``scoring="softmax"``:
     scores = softmax over all experts' logits; the ``top`` largest of score + ``pick_bias`` (a float32 correction per
-    expert, or None) are chosen; weights = the chosen scores * ``scale`` as they are. Then the (token, choice)
+    expert, or None) are chosen; weights = the chosen scores * ``scale`` as they are. ``scoring="softmax_norm"``: the
+    same scores and choice; weights = score / (the chosen scores' sum + 1e-20) * ``scale``. Then the (token, choice)
     pairs are laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order
     [T * top] (the pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]. ``logits``: float32
     scratch [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k
@@ -1001,7 +1002,7 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
     E = w_router.shape[0]
     _need(h.dtype in DT and w_router.dtype == torch.float32 and w_router.shape == (E, d), "moe_route: input or router matrix")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "moe_route: bias")
-    _need(pick_bias is None or (pick_bias.dtype == torch.float32 and pick_bias.numel() == E and scoring == "softmax"),
+    _need(pick_bias is None or (pick_bias.dtype == torch.float32 and pick_bias.numel() == E and scoring in ("softmax", "softmax_norm")),
           "moe_route: the choice correction is float32, one per expert, and goes with the softmax scoring")
     _need(scoring in ROUTE_SCORINGS, f"moe_route: scoring {scoring!r} is not one of {sorted(ROUTE_SCORINGS)}")
     for t in (choice, rank, place, order):
@@ -1055,3 +1056,209 @@ def moe_experts_tc(h, w_gate_up, w_down, order, place, weight, tiles, xs, act, y
     lib().call("slb_moe_experts_tc", _p(h), _p(w_gate_up), _p(w_down), _p(order), _p(place), _p(weight), _p(tiles), _p(xs),
                _p(act), _p(y), _p(x), T, d, ff, E, int(top), ACTIVATIONS[activation], float(limit), float(alpha),
                _p(_tc_status(h.device)), stream if stream is not None else current_stream())
+
+
+# ---- other score rules, short convolutions, recurrences with a matrix state, several copies of the stream ----
+
+def _st(stream):
+    return stream if stream is not None else current_stream()
+
+
+def _rows_f32(t, width: int, what: str) -> int:
+    """``t`` is a float32 matrix (possibly a view of a wider one) whose rows hold at least ``width`` values; its row stride."""
+    _need(t.is_cuda and t.dtype == torch.float32 and t.dim() == 2 and t.shape[1] >= width and (t.shape[1] == 0 or t.stride(1) == 1),
+          f"{what}: float32 rows of at least {width} values (possibly a view of a wider matrix)")
+    return t.stride(0) if t.shape[0] > 1 else max(t.shape[1], width)
+
+
+def attention_scored(q, k_pool, v_pool, out, tok_seq, tok_pos, block_table, heads: int, kv_heads: int, head_dim: int,
+                     window: int, scale: float, stream=None, slopes=None, softcap: float = 0.0, maps: int = 1, gate=None,
+                     value_dim: int = 0) -> None:
+    """The general attention kernel with other score rules. ``slopes`` [heads] float32: the score loses
+    slopes[h] * (query position - key position). ``softcap`` c > 0: score <- c tanh(score / c) before that. ``maps`` m > 1:
+    every head has m score maps over the same values; q is [T, heads * m, head_dim], a key row of the cache is m * head_dim
+    wide, and ``out`` is float32 [T, heads * m, value_dim]. ``gate``: float32 [T, >= heads * value_dim] pre-activations;
+    the result is multiplied by their sigmoid (one map only)."""
+    _cuda(q, k_pool, v_pool, out, tok_seq, tok_pos, block_table, slopes)
+    T = q.shape[0]
+    vd = value_dim or head_dim
+    _need(q.shape == (T, heads * maps, head_dim) and out.numel() == T * heads * maps * vd, "attention_scored: shapes disagree")
+    _need(q.dtype == k_pool.dtype == v_pool.dtype and q.dtype in DT, "attention_scored: dtypes")
+    _need(out.dtype == (torch.float32 if maps > 1 else q.dtype), "attention_scored: several maps give a float32 result")
+    _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, maps * head_dim) and tuple(v_pool.shape[1:]) == (kv_heads, 64, vd)
+          and k_pool.shape[0] == v_pool.shape[0], "attention_scored: pool shape")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "attention_scored: block table")
+    _need(slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == heads), "attention_scored: slopes are float32, one per head")
+    gs = 0
+    if gate is not None:
+        _need(maps == 1, "attention_scored: the gate goes with one map")
+        gs = _rows_f32(gate, heads * vd, "attention_scored gate")
+    lib().call("slb_attention_scored", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(tok_seq), _p(tok_pos), _p(block_table),
+               block_table.shape[1], T, heads, kv_heads, head_dim, int(window), float(scale), _p(slopes), float(softcap),
+               int(maps), 1 if maps > 1 else 0, _p(gate), gs, vd, DT[q.dtype], _st(stream))
+
+
+def causal_conv(u, weight, bias, state, slots, tok_seq, seq_start, out, act: bool = False, stream=None) -> None:
+    """out[t, c] = sum_j weight[c, j] * u_(t - taps + 1 + j)[c] (+ bias[c]; silu with ``act``) over each sequence's tokens
+    of the step; inputs in front of the step come from ``state`` [slots, taps - 1, C] (the sequence's last inputs, zeros
+    at its start), which is then brought up to date. ``u`` and ``out`` are float32 rows, possibly views of wider ones."""
+    _cuda(weight, bias, state, slots, tok_seq, seq_start)
+    C, taps = weight.shape
+    T = u.shape[0]
+    us, os_ = _rows_f32(u, C, "causal_conv input"), _rows_f32(out, C, "causal_conv output")
+    _need(weight.dtype == torch.float32 and (bias is None or (bias.dtype == torch.float32 and bias.numel() == C)), "causal_conv: taps and bias are float32")
+    _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (max(taps - 1, 0), C) or taps == 1, "causal_conv: state [slots, taps - 1, channels]")
+    _need(out.shape[0] == T and slots.dtype == torch.int32 and tok_seq.dtype == torch.int32 and seq_start.dtype == torch.int32, "causal_conv: tables")
+    lib().call("slb_causal_conv", _p(u), us, _p(weight), _p(bias), _p(state), _p(slots), _p(tok_seq), _p(seq_start), _p(out), os_,
+               T, slots.numel(), C, taps, 1 if act else 0, _st(stream))
+
+
+def decay_scan(q, k, v, a, state, slots, seq_start, out, heads: int, groups: int, per_channel: bool, v_scale=None,
+               q_scale: float = 1.0, stream=None) -> None:
+    """Per head S_t = diag(a_t) S_(t-1) + k_t v_t^T and out_t = S_t^T q_t * ``q_scale`` over each sequence's tokens of the
+    step, from and back into ``state`` float32 [slots, heads, N, P]. q, k: float32 rows of groups * N values (head h reads
+    group h // (heads / groups)); v: rows of heads * P values, times ``v_scale`` [T, heads] when given; a: rows of
+    heads * N decays (``per_channel``) or of one decay a head. out: float32 [T, heads * P]."""
+    _cuda(state, slots, seq_start, out)
+    _, H, N, P = state.shape
+    T = out.shape[0]
+    _need(H == heads and heads % groups == 0 and state.dtype == torch.float32 and out.dtype == torch.float32
+          and out.shape == (T, heads * P), "decay_scan: state or output")
+    qs, ks = _rows_f32(q, groups * N, "decay_scan q"), _rows_f32(k, groups * N, "decay_scan k")
+    vs_ = _rows_f32(v, heads * P, "decay_scan v")
+    as_ = _rows_f32(a, heads * N if per_channel else heads, "decay_scan a")
+    ss = _rows_f32(v_scale, heads, "decay_scan v_scale") if v_scale is not None else 0
+    _need(slots.dtype == torch.int32 and seq_start.dtype == torch.int32 and seq_start.numel() >= slots.numel() + 1, "decay_scan: tables")
+    lib().call("slb_decay_scan", _p(q), qs, _p(k), ks, _p(v), vs_, _p(a), as_, 1 if per_channel else 0, _p(v_scale), ss, _p(state),
+               _p(slots), _p(seq_start), _p(out), slots.numel(), heads, groups, N, P, float(q_scale), _st(stream))
+
+
+def step_decay(raw, dt_bias, a_log, dt, decay, stream=None) -> None:
+    """dt = softplus(raw + dt_bias), decay = exp(-exp(a_log) * dt), per (token, head); raw: float32 rows of ``heads`` values."""
+    _cuda(dt_bias, a_log, dt, decay)
+    T, H = dt.shape
+    rs = _rows_f32(raw, H, "step_decay")
+    _need(dt.dtype == decay.dtype == dt_bias.dtype == a_log.dtype == torch.float32 and decay.shape == dt.shape and dt_bias.numel() == H
+          and a_log.numel() == H and raw.shape[0] == T, "step_decay: float32 [tokens, heads]")
+    lib().call("slb_step_decay", _p(raw), rs, _p(dt_bias), _p(a_log), _p(dt), _p(decay), T, H, _st(stream))
+
+
+def channel_decay(z, bias, tau: float, stream=None) -> None:
+    """z <- sigmoid(z + bias)^(1 / tau) in place; z float32 [T, C] contiguous."""
+    _cuda(z, bias)
+    T, C = z.shape
+    _need(z.dtype == torch.float32 and (bias is None or (bias.dtype == torch.float32 and bias.numel() == C)), "channel_decay: float32")
+    lib().call("slb_channel_decay", _p(z), _p(bias), T, C, float(tau), _st(stream))
+
+
+def gated_group_norm(y, gate, gain, out, groups: int, eps: float, gate_first: bool, skip=None, skip_gain=None,
+                     head_width: int = 1, stream=None) -> None:
+    """Rows of ``y`` float32 [T, inner] in ``groups`` equal parts, each divided by its root mean square, times
+    gain[c % len(gain)]; silu(gate) multiplies the row before the norm (``gate_first``) or after it. With ``skip``:
+    skip_gain[c // head_width] * skip[t, c] is added to y first. ``out`` [T, inner] in the run dtype."""
+    _cuda(y, gain, out, skip_gain)
+    T, inner = y.shape
+    gs = _rows_f32(gate, inner, "gated_group_norm gate")
+    ks = _rows_f32(skip, inner, "gated_group_norm skip") if skip is not None else 0
+    _need(y.dtype == torch.float32 and gain.dtype == torch.float32 and out.shape == (T, inner) and out.dtype in DT and inner % groups == 0,
+          "gated_group_norm: shapes or dtypes")
+    _need(skip is None or (skip_gain is not None and skip_gain.dtype == torch.float32 and skip_gain.numel() * head_width == inner),
+          "gated_group_norm: the skip term's gains")
+    lib().call("slb_gated_group_norm", _p(y), _p(skip), ks, _p(skip_gain), int(head_width), _p(gate), gs, _p(gain), gain.numel(),
+               _p(out), T, inner, int(groups), 1 if gate_first else 0, float(eps), DT[out.dtype], _st(stream))
+
+
+def unit_post(rows, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table, heads: int, kv_heads: int,
+              maps: int, dim: int, vdim: int, rot: int, eps: float, stream=None) -> None:
+    """float32 rows [q units | k units | v units] -> q_out [T, heads * maps, dim] and the token's cache rows (keys
+    [pages, kv_heads, 64, maps * dim], values [pages, kv_heads, 64, vdim]); without pools the rows hold q units only.
+    q and k units: RMS norm with the gain when one is given, then the first ``rot`` channels turn in pairs (i, i + rot/2)."""
+    _cuda(q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table)
+    T = q_out.shape[0]
+    writes = k_pool is not None
+    width = heads * maps * dim + (kv_heads * maps * dim + kv_heads * vdim if writes else 0)
+    rs = _rows_f32(rows, width, "unit_post")
+    _need(q_out.shape == (T, heads * maps, dim) and q_out.dtype in DT and rows.shape[0] == T, "unit_post: the query buffer")
+    for g in (q_gain, k_gain):
+        _need(g is None or (g.dtype == torch.float32 and g.numel() == dim), "unit_post: gains are float32 [dim]")
+    if rot:
+        _need(cos is not None and cos.dtype == torch.float32 and cos.shape[1] == rot // 2 and sin.shape == cos.shape, "unit_post: rotation tables")
+    stride = 0
+    if writes:
+        _need(k_pool.dtype == v_pool.dtype == q_out.dtype and tuple(k_pool.shape[1:]) == (kv_heads, 64, maps * dim)
+              and tuple(v_pool.shape[1:]) == (kv_heads, 64, vdim), "unit_post: cache pools")
+        _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "unit_post: block table")
+        stride = block_table.shape[1]
+    lib().call("slb_unit_post", _p(rows), rs, _p(q_gain), _p(k_gain), _p(cos), _p(sin), _p(q_out), _p(k_pool), _p(v_pool),
+               _p(tok_seq), _p(tok_pos), _p(block_table) if writes else None, stride, T, heads, kv_heads, maps, dim, vdim, int(rot),
+               1 if writes else 0, float(eps), DT[q_out.dtype], _st(stream))
+
+
+def diff_combine(a, gate, out, heads: int, vdim: int, lam: float, post: float, eps: float, stream=None) -> None:
+    """out[t, h] = (a[t, h, 0] - lam * a[t, h, 1]) / rms * post * sigmoid(gate[t, h]); a float32 [T, heads * 2, vdim]."""
+    _cuda(a, out)
+    T = out.shape[0]
+    _need(a.dtype == torch.float32 and a.numel() == T * heads * 2 * vdim and out.shape == (T, heads * vdim) and out.dtype in DT, "diff_combine: shapes")
+    gs = _rows_f32(gate, heads, "diff_combine gate") if gate is not None else 0
+    lib().call("slb_diff_combine", _p(a), _p(gate), gs, _p(out), T, heads, vdim, float(lam), float(post), float(eps), DT[out.dtype], _st(stream))
+
+
+def streams_fill(x0, xs, streams: int, stream=None) -> None:
+    """xs [T, streams * d] <- every copy the row of x0 [T, d] (float32)."""
+    _cuda(x0, xs)
+    T, d = x0.shape
+    _need(x0.dtype == xs.dtype == torch.float32 and xs.shape == (T, streams * d), "streams_fill: shapes")
+    lib().call("slb_streams_fill", _p(x0), _p(xs), T, d, int(streams), _st(stream))
+
+
+def hyper_read(xs, coef, gain, out, eps: float, stream=None) -> None:
+    """out[t] = RMS norm of sum_s coef[s] xs[t, s] (ones without ``coef``), times gain, in the run dtype."""
+    _cuda(xs, coef, gain, out)
+    T, d = out.shape
+    S = xs.shape[1] // d
+    _need(xs.dtype == torch.float32 and xs.shape == (T, S * d) and gain.dtype == torch.float32 and gain.numel() == d and out.dtype in DT, "hyper_read: shapes")
+    _need(coef is None or (coef.dtype == torch.float32 and coef.numel() == S), "hyper_read: one coefficient a copy")
+    lib().call("slb_hyper_read", _p(xs), _p(coef), _p(gain), _p(out), T, d, S, float(eps), DT[out.dtype], _st(stream))
+
+
+def hyper_write(xs, y, mix, out_coef, mult: float, stream=None) -> None:
+    """xs[t, r] <- sum_s mix[s, r] xs[t, s] + mult * out_coef[r] * y[t], all copies from the old ones (identity and ones
+    without ``mix`` / ``out_coef``)."""
+    _cuda(xs, y, mix, out_coef)
+    T, d = y.shape
+    S = xs.shape[1] // d
+    _need(xs.dtype == y.dtype == torch.float32 and xs.shape == (T, S * d), "hyper_write: shapes")
+    _need(mix is None or (mix.dtype == torch.float32 and mix.shape == (S, S)), "hyper_write: the mixing matrix")
+    _need(out_coef is None or (out_coef.dtype == torch.float32 and out_coef.numel() == S), "hyper_write: one coefficient a copy")
+    lib().call("slb_hyper_write", _p(xs), _p(y), _p(mix), _p(out_coef), T, d, S, float(mult), _st(stream))
+
+
+def streams_sum(xs, x, stream=None) -> None:
+    _cuda(xs, x)
+    T, d = x.shape
+    S = xs.shape[1] // d
+    _need(xs.dtype == x.dtype == torch.float32 and xs.shape == (T, S * d), "streams_sum: shapes")
+    lib().call("slb_streams_sum", _p(xs), _p(x), T, d, S, _st(stream))
+
+
+def pair_combine(a, b, target, gain_a=None, gain_b=None, scale_a: float = 1.0, scale_b: float = 1.0, eps: float = 0.0,
+                 accumulate: bool = True, stream=None) -> None:
+    """target (+)= scale_a * a + scale_b * b; with gains each row is first divided by its own root mean square and
+    multiplied by its gain. All float32 [T, d]."""
+    _cuda(a, b, target, gain_a, gain_b)
+    T, d = a.shape
+    _need(a.dtype == b.dtype == target.dtype == torch.float32 and b.shape == a.shape == target.shape, "pair_combine: shapes")
+    for g in (gain_a, gain_b):
+        _need(g is None or (g.dtype == torch.float32 and g.numel() == d), "pair_combine: gains")
+    lib().call("slb_pair_combine", _p(a), _p(b), _p(gain_a), _p(gain_b), float(scale_a), float(scale_b), float(eps), _p(target), T, d,
+               1 if accumulate else 0, _st(stream))
+
+
+def row_gate(h, w, y, target, accumulate: bool = True, stream=None) -> None:
+    """target[t] (+)= sigmoid(h[t] . w) * y[t]; h [T, k] in the run dtype, w float32 [k], y and target float32 [T, d]."""
+    _cuda(h, w, y, target)
+    T, k = h.shape
+    d = y.shape[1]
+    _need(h.dtype in DT and w.dtype == torch.float32 and w.numel() == k and y.dtype == target.dtype == torch.float32
+          and y.shape == target.shape == (T, d), "row_gate: shapes")
+    lib().call("slb_row_gate", _p(h), _p(w), _p(y), _p(target), T, k, d, 1 if accumulate else 0, DT[h.dtype], _st(stream))

@@ -249,6 +249,77 @@ class SandwichLayer(Part):
         ws.release(mark)
 
 
+class HyperLayer(Part):
+    """Hyper-connections: the stream is ``streams`` copies [tokens, streams * hidden]. Sublayer q reads the copies' weighted
+    sum through its norm (one kernel), delivers into an empty float32 buffer, and one kernel then rewrites all copies:
+    x_r <- sum_s mix[s, r] x_s + mult * out[r] * y. With ``streams`` 0 there is one copy and no coefficients: the plain
+    pre-norm layer with a multiplier on each sublayer's result. The norms must be RMS norms. The feed-forward may be absent."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext):
+        self.ctx, self.streams, self.mult = ctx, int(spec.streams), float(spec.residual_mult)
+        self.hidden = spec.norm1.dim
+        self.norm1 = build_norm(spec.norm1, ctx)
+        self.mixer = build_mixer(spec.mixer, ctx)
+        self.ffn = build_ffn(spec.ffn, ctx) if spec.ffn is not None else None
+        self.children = {"norm1": self.norm1, "mixer": self.mixer}
+        if self.ffn is not None:
+            self.norm2 = build_norm(spec.norm2, ctx)
+            self.children.update({"norm2": self.norm2, "ffn": self.ffn})
+        for name, part in self.children.items():
+            if name.startswith("norm") and not getattr(part, "fusable", False):
+                raise ValueError("hyper layer: its norms must be RMS norms")
+        if self.streams > 8:
+            raise ValueError(f"hyper layer: at most 8 copies of the stream, got {self.streams}")
+        self.coef = {}
+        self.capturable = all(getattr(p, "capturable", True) for p in self.children.values())
+
+    def declare(self):
+        out = PreNormLayer.declare(self)
+        if self.streams:
+            for q in ("1", "2") if self.ffn is not None else ("1",):
+                out[f"hc{q}.in"] = ParamDecl((self.streams,), "vector", init="gain")
+                out[f"hc{q}.out"] = ParamDecl((self.streams,), "vector", init="gain")
+                out[f"hc{q}.mix"] = ParamDecl((self.streams, self.streams), "vector")
+        return out
+
+    def bind(self, tensors):
+        PreNormLayer.bind(self, tensors)
+        self.coef = {k: v.to(torch.float32).contiguous() for k, v in tensors.items() if k.startswith("hc")}
+
+    cache_request = PreNormLayer.cache_request
+
+    def lead_weight(self):
+        return lead_weight_of(self.mixer)
+
+    def forward(self, x, b, view, ws):
+        after = getattr(b, "next_read", None)
+        self._sublayer("1", self.norm1, self.mixer, x, b, ws, view, lead_weight_of(self.ffn) if self.ffn is not None else after)
+        if self.ffn is not None:
+            self._sublayer("2", self.norm2, self.ffn, x, b, ws, None, after)
+        b.next_read = after
+
+    def _sublayer(self, q, norm, part, x, b, ws, view, after):
+        mark = ws.mark()
+        T = x.shape[0]
+        h = ws.take((T, self.hidden), self.ctx.dtype)
+        ops.hyper_read(x, self.coef.get(f"hc{q}.in"), norm.weight, h, norm.eps, b.stream)
+        y = ws.take((T, self.hidden), torch.float32)
+        if getattr(part, "stores_result", False):
+            b.store_first = True
+        else:
+            y.zero_()
+        b.next_read = after
+        if part is self.mixer:
+            part.forward(h, y, b, view, ws)
+        else:
+            part.forward(h, y, b, ws)
+        if getattr(b, "store_first", False):
+            raise RuntimeError(f"{type(part).__name__} says it stores its result and did not")
+        ops.hyper_write(x, y, self.coef.get(f"hc{q}.mix"), self.coef.get(f"hc{q}.out"), self.mult, b.stream)
+        ws.release(mark)
+
+
+register_layer("hyper", HyperLayer)
 register_layer("sandwich", SandwichLayer)
 register_layer("prenorm", PreNormLayer)
 register_layer("parallel", ParallelLayer)

@@ -41,7 +41,9 @@ class RoutedExperts(Part):
             raise ValueError(f"routed_experts: scoring {spec.scoring!r} is not one of {sorted(ops.ROUTE_SCORINGS)}")
         if spec.groups < 1 or spec.experts % spec.groups or not 1 <= spec.keep_groups <= spec.groups:
             raise ValueError(f"routed_experts: {spec.experts} experts in {spec.groups} groups of which {spec.keep_groups} are kept")
-        if spec.choice_bias and spec.scoring != "softmax":
+        if spec.shared_gate and spec.shared is None:
+            raise ValueError("routed_experts: a gate on the shared expert needs a shared expert")
+        if spec.choice_bias and spec.scoring not in ("softmax", "softmax_norm"):
             raise ValueError("routed_experts: a choice correction goes with the softmax scoring over all experts")
         if spec.groups > 1 and spec.scoring != "sigmoid":
             raise ValueError("routed_experts: groups of experts go with the sigmoid scoring")
@@ -70,6 +72,8 @@ class RoutedExperts(Part):
         if self.shared is not None:
             for name, decl in self.shared.declare().items():
                 d["shared." + name] = decl
+        if s.shared_gate:
+            d["shared_gate"] = ParamDecl((1, s.hidden), "vector")
         return d
 
     def bind(self, t):
@@ -82,6 +86,7 @@ class RoutedExperts(Part):
         self.w_down = torch.stack([t[f"e{e}.down.weight"] for e in range(s.experts)]).to(dt).contiguous()
         if self.shared is not None:
             self.shared.bind({k[len("shared."):]: v for k, v in t.items() if k.startswith("shared.")})
+        self.w_shared_gate = t["shared_gate"].to(torch.float32).reshape(-1).contiguous() if s.shared_gate else None
         # A bfloat16 run whose router matrix is exactly representable in bfloat16 (a file that stores it so) forms the
         # logits as a product of its own: bfloat16 times bfloat16 is exact in float32 and the sums are float32, so these
         # are the float32 logits of the same inputs, from the tensor cores instead of a lane per token.
@@ -99,14 +104,25 @@ class RoutedExperts(Part):
         s, dt = self.spec, self.ctx.dtype
         if isinstance(h, Normed):
             h = h.tensor()
+        mark = ws.mark()
         if self.shared is not None:       # the shared expert first: its weights are what the layer in front asked L2 for
             after = getattr(b, "next_read", None)
             b.next_read = None
-            self.shared.forward(h, x, b, ws)
+            if self.w_shared_gate is None:
+                self.shared.forward(h, x, b, ws)
+            else:                         # its result times sigmoid(w . h), one number a token, joins the stream in one kernel
+                store = bool(getattr(b, "store_first", False))
+                own = ws.take(x.shape, torch.float32)
+                if getattr(self.shared, "stores_result", False):
+                    b.store_first = True
+                else:
+                    b.store_first = False
+                    own.zero_()
+                self.shared.forward(h, own, b, ws)
+                ops.row_gate(h, self.w_shared_gate, own, x, accumulate=not store, stream=b.stream)
             b.next_read = after
         T = h.shape[0]
         pairs = T * s.top
-        mark = ws.mark()
         choice, rank, place, order = (ws.take((pairs,), torch.int32) for _ in range(4))
         counts = ws.take((s.experts,), torch.int32)
         weight = ws.take((pairs,), torch.float32)

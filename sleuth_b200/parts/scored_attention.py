@@ -1,0 +1,145 @@
+"""Causal grouped-query attention with other score rules, as a mixer part (``ScoredAttentionSpec``).
+
+One stacked projection [q | k | v | gate] with a float32 result; then, as the spec asks: a short causal convolution over
+time on the q, k and v channels (``ops.causal_conv``; a sequence's last taps - 1 projected values are state); per-unit RMS
+norm, rotation and the cache write (``ops.unit_post``); attention over the paged cache by the general kernel with a soft
+cap, a distance penalty per head, a window, and one or two score maps a head (``ops.attention_scored``); for two maps the
+difference a1 - lambda a2 with its norm and the head gates (``ops.diff_combine``); the output projection into the stream.
+
+The entry keeps keys and values in pages (a key row is ``maps * head_dim`` wide, so both maps' keys of a position lie
+together) and, with a convolution, the tails of the projected rows per sequence. A part that ``reads_shared_kv`` has no key
+and value tensors: it reads the entry its schedule entry borrows and keeps only its own query tails.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.paged import BundleRequest, KVRequest, StateRequest
+from ..kernels import ops
+from .base import BuildContext, Normed, ParamDecl, Part, build_position, register_mixer, result_target
+from .linear import Linear
+from .spec import ScoredAttentionSpec
+
+
+class ScoredAttention(Part):
+    stores_result = True
+
+    def __init__(self, spec: ScoredAttentionSpec, ctx: BuildContext):
+        s = spec
+        if s.heads % s.kv_heads:
+            raise ValueError(f"heads ({s.heads}) must be a multiple of kv_heads ({s.kv_heads})")
+        if s.head_dim % 2 or s.head_dim > 256 or s.value_dim > 256 or s.value_dim < 1:
+            raise ValueError(f"scored attention: head_dim {s.head_dim} (even, at most 256), value_dim {s.value_dim} (at most 256)")
+        if s.maps not in (1, 2):
+            raise ValueError(f"scored attention: one score map a head or two (differential), not {s.maps}")
+        if s.gate not in ("none", "channel", "head"):
+            raise ValueError(f"scored attention: gate {s.gate!r} is not 'none', 'channel' or 'head'")
+        if s.gate == "channel" and s.maps != 1 or s.gate == "head" and s.maps != 2:
+            raise ValueError("scored attention: a gate per channel goes with one map, a gate per head with two")
+        if not 0 <= s.conv_taps <= 16:
+            raise ValueError(f"scored attention: conv_taps {s.conv_taps} (at most 16)")
+        self.spec, self.ctx = spec, ctx
+        self.position = build_position(s.position, ctx)
+        self.scale = s.scale or 1.0 / math.sqrt(s.head_dim)
+        self.nq = s.heads * s.maps * s.head_dim
+        self.nk = 0 if s.reads_shared_kv else s.kv_heads * s.maps * s.head_dim
+        self.nv = 0 if s.reads_shared_kv else s.kv_heads * s.value_dim
+        self.ng = {"none": 0, "channel": s.heads * s.value_dim, "head": s.heads}[s.gate]
+        self.slopes = None
+        if s.slope_exponent > 0:
+            self.slopes = torch.tensor([2.0 ** (-s.slope_exponent * (h + 1) / s.heads) for h in range(s.heads)],
+                                       dtype=torch.float32, device=ctx.device)
+        self.qkvg = self.o = self.conv = self.q_gain = self.k_gain = None
+        self.lam = 0.0
+
+    def _proj(self):
+        return ["q"] if self.spec.reads_shared_kv else ["q", "k", "v"]
+
+    def declare(self):
+        s = self.spec
+        d = {"q.weight": ParamDecl((self.nq, s.hidden)), "o.weight": ParamDecl((s.hidden, s.heads * s.value_dim))}
+        if not s.reads_shared_kv:
+            d["k.weight"] = ParamDecl((self.nk, s.hidden))
+            d["v.weight"] = ParamDecl((self.nv, s.hidden))
+        if s.conv_taps:
+            for n, rows in (("q", self.nq), ("k", self.nk), ("v", self.nv)):
+                if rows:
+                    d[f"{n}.conv"] = ParamDecl((rows, s.conv_taps), "vector")
+        if s.qk_norm:
+            d["q_norm.weight"] = ParamDecl((s.head_dim,), "vector", init="gain")
+            if not s.reads_shared_kv:
+                d["k_norm.weight"] = ParamDecl((s.head_dim,), "vector", init="gain")
+        if s.gate != "none":
+            d["g.weight"] = ParamDecl((self.ng, s.hidden))
+        if s.maps == 2:
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                d[n] = ParamDecl((s.head_dim,), "vector")
+        return d
+
+    def bind(self, t):
+        s, dt = self.spec, self.ctx.dtype
+        stack = [t[n + ".weight"] for n in self._proj()] + ([t["g.weight"]] if self.ng else [])
+        self.qkvg = Linear(torch.cat(stack, dim=0), dt)
+        self.o = Linear(t["o.weight"], dt)
+        if s.conv_taps:
+            self.conv = torch.cat([t[n + ".conv"] for n in self._proj()], dim=0).to(torch.float32).contiguous()
+        if s.qk_norm:
+            self.q_gain = t["q_norm.weight"].to(torch.float32).contiguous()
+            self.k_gain = None if s.reads_shared_kv else t["k_norm.weight"].to(torch.float32).contiguous()
+        if s.maps == 2:
+            f = {n: t[n].to(torch.float32) for n in ("lq1", "lk1", "lq2", "lk2")}
+            self.lam = float(torch.exp((f["lq1"] * f["lk1"]).sum()) - torch.exp((f["lq2"] * f["lk2"]).sum())) + s.diff
+
+    def cache_request(self):
+        s = self.spec
+        parts = []
+        if not s.reads_shared_kv:
+            parts.append(("kv", KVRequest(s.kv_heads, s.maps * s.head_dim, s.window, s.value_dim)))
+        if s.conv_taps > 1:
+            parts.append(("tail", StateRequest((s.conv_taps - 1, self.nq + self.nk + self.nv), torch.float32)))
+        return BundleRequest(tuple(parts)) if parts else None
+
+    def lead_weight(self):
+        return self.qkvg.weight if self.qkvg is not None else None
+
+    def forward(self, h, x, b, view, ws):
+        s, dt = self.spec, self.ctx.dtype
+        if isinstance(h, Normed):
+            h = h.tensor()
+        T = h.shape[0]
+        mark = ws.mark()
+        kv = view["borrowed"]["kv"] if s.reads_shared_kv else view["kv"]
+        writes = kv.writes and not s.reads_shared_kv
+        table = b.tables[kv.group]
+        p = self.qkvg.forward(h, ws=ws, stream=b.stream, out_dtype=torch.float32)
+        nqkv = self.nq + self.nk + self.nv
+        rows = p
+        if self.conv is not None:
+            rows = ws.take((T, nqkv), torch.float32)
+            ops.causal_conv(p, self.conv, None, view["tail"].state, b.slots, b.tok_seq, b.seq_start, rows, False, b.stream)
+        tables = self.position.tables()
+        cos, sin = tables if tables is not None else (None, None)
+        q = ws.take((T, s.heads * s.maps, s.head_dim), dt)
+        ops.unit_post(rows, self.q_gain, self.k_gain, cos, sin, q, kv.k_pool if writes else None, kv.v_pool if writes else None,
+                      b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads, s.maps, s.head_dim, s.value_dim,
+                      self.position.rot_dim, s.eps, b.stream)
+        gate = p[:, nqkv:] if self.ng else None
+        y = ws.take((T, s.heads * s.value_dim), dt)
+        if s.maps == 1:
+            ops.attention_scored(q, kv.k_pool, kv.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads, s.head_dim,
+                                 kv.window, self.scale, b.stream, slopes=self.slopes, softcap=s.softcap, gate=gate,
+                                 value_dim=s.value_dim)
+        else:
+            a = ws.take((T, s.heads * 2, s.value_dim), torch.float32)
+            ops.attention_scored(q, kv.k_pool, kv.v_pool, a, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads, s.head_dim,
+                                 kv.window, self.scale, b.stream, slopes=self.slopes, softcap=s.softcap, maps=2,
+                                 value_dim=s.value_dim)
+            ops.diff_combine(a, gate, y, s.heads, s.value_dim, self.lam, 1.0 - s.diff, s.eps, b.stream)
+        self.o.forward(y, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None), **result_target(b, x))
+        ws.release(mark)
+
+
+register_mixer("scored_attention", ScoredAttention)

@@ -34,13 +34,17 @@ class PositionSpec:
     """Position encoding applied to queries and keys. ``kind="rotary"``: the first ``rotary_dim`` channels of each
     head turn in pairs by the angle position * theta^(-2i/rotary_dim) of pair i; ``pairing="halves"`` pairs channel i
     with i + rotary_dim/2, ``pairing="neighbours"`` channel 2i with 2i + 1. ``kind="none"``: nothing.
-    ``precise``: the tables are worked out in 64-bit and rounded once (otherwise in float32, operation by operation)."""
+    ``precise``: the tables are worked out in 64-bit and rounded once (otherwise in float32, operation by operation).
+    ``scaling`` = (factor, low, high, original): frequencies are rescaled band by band. With wavelength l = 2 pi / f a
+    frequency stays where l < original / high, becomes f / factor where l > original / low, and between the two
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
     head_dim: int
     theta: float = 10000.0
     rotary_dim: int = 0          # 0 = all of head_dim
     kind: str = "rotary"
     pairing: str = "halves"
     precise: bool = False
+    scaling: tuple = ()
 
 
 @dataclass(frozen=True)
@@ -62,6 +66,89 @@ class AttentionSpec:
     qk_norm_span: str = "head"   # "head": one RMSNorm per head, gains [head_dim]; "projection": one over all heads of q
                                  # (and one over all heads of k) before they are split, gains of the projection's length
     sinks: bool = False          # a learned score per head joins the softmax denominator (no key, no value, unscaled)
+
+
+@dataclass(frozen=True)
+class ScoredAttentionSpec:
+    """Causal grouped-query attention over the key/value cache with other score rules and other post-processing than
+    ``AttentionSpec``'s. q = W_q h (``heads`` * ``maps`` units of ``head_dim``), k = W_k h (``kv_heads`` * ``maps`` units),
+    v = W_v h (``kv_heads`` units of ``value_dim``); then, each optional and in this order: a short causal convolution over
+    time on every channel of q, k and v (``conv_taps`` taps, tensors ``q.conv`` ...; the last taps - 1 projected values of a
+    sequence are state); an RMS norm of every q and k unit with a gain of ``head_dim`` values (``qk_norm``); rotation of
+    the first channels of every q and k unit (``position``). score = q . k * ``scale``; ``softcap`` c: c tanh(score / c);
+    ``slope_exponent`` e > 0: the score loses 2^(-e (h + 1) / heads) * (i - j) for head h; ``window`` as for
+    ``AttentionSpec``. ``maps`` = 2: differential attention, two softmax maps a head over the same values, o = a1 -
+    lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ``diff`` (four tensors of ``head_dim`` values), then o
+    divided by its root mean square over ``value_dim`` and multiplied by 1 - ``diff``. ``gate``: "channel" multiplies the
+    concatenated heads by sigmoid(W_g h), "head" multiplies head h by sigmoid(W_g h)_h, "none" nothing.
+    ``reads_shared_kv``: no key and value tensors; the application reads the cache entry that its schedule entry borrows."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    value_dim: int
+    position: PositionSpec
+    scale: float
+    eps: float = 1e-6
+    conv_taps: int = 0
+    qk_norm: bool = False
+    softcap: float = 0.0
+    slope_exponent: float = 0.0
+    window: int = 0
+    maps: int = 1
+    diff: float = 0.0
+    gate: str = "none"
+    reads_shared_kv: bool = False
+    kind: str = "scored_attention"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """The state-space-duality recurrence (Mamba-2). inner = ``heads`` * ``value_dim``; W_in h = [z: inner | x: inner |
+    B: groups * state | C: groups * state | dt: heads]. x, B and C pass a causal convolution per channel (``conv_taps``
+    taps with a bias) and silu. dt = softplus(dt + dt_bias); per head (head h reads group h // (heads / groups)) the
+    ``state`` x ``value_dim`` matrix S_t = exp(-exp(A_log_h) dt) S_(t-1) + dt B_t x_t^T, y_t = S_t^T C_t + D_h x_t. y times
+    silu(z), RMS-normed in ``norm_groups`` equal parts with a gain per channel, then W_o."""
+    hidden: int
+    heads: int
+    value_dim: int
+    state: int
+    groups: int = 1
+    conv_taps: int = 4
+    norm_groups: int = 1
+    eps: float = 1e-6
+    kind: str = "state_space"
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention with a decay per key channel. q = W_q h * head_dim^(-1/2), k = W_k h (``heads`` x ``head_dim``),
+    v = W_v h (``heads`` x ``value_dim``); alpha = sigmoid(W_a2 (W_a1 h) + b)^(1 / ``tau``), one factor per key channel.
+    Per head S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t; each head's o RMS-normed over ``value_dim`` with a
+    gain shared by the heads, the heads times silu(W_g h), then W_o."""
+    hidden: int
+    heads: int
+    head_dim: int
+    value_dim: int
+    decay_rank: int
+    tau: float
+    eps: float = 1e-6
+    kind: str = "gated_linear_attention"
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same input; tensors of the first under ``left.``, of the second under ``right.``.
+    ``combine="normed_mean"``: half the sum of the two results, each first RMS-normed over the model width with a gain of
+    its own (tensors ``left_out``, ``right_out``). ``combine="scaled"``: left_scale * left + right_scale * right."""
+    hidden: int
+    left: object
+    right: object
+    combine: str = "scaled"
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    eps: float = 1e-6
+    kind: str = "side_by_side"
 
 
 @dataclass(frozen=True)
@@ -123,7 +210,8 @@ class RoutedExpertsSpec:
     can be chosen; the ``top`` largest scores, weights = score / (their sum + 1e-20) * ``route_scale``.
     ``scoring="softmax"``: scores = softmax over all experts' logits; the ``top`` largest of score + correction are chosen
     (``choice_bias``: the tensor ``correction``, one value per expert, moves the choice and never the weights); weights = the chosen
-    experts' scores * ``route_scale`` as they are (no division by their sum).
+    experts' scores * ``route_scale`` as they are (no division by their sum). ``scoring="softmax_norm"``: the same scores and
+    choice; weights = score / (the chosen scores' sum + 1e-20) * ``route_scale``.
     ``activation``, ``limit``, ``alpha``: as for ``GatedMLPSpec``. ``shared``: a gated feed-forward (a ``GatedMLPSpec``)
     that every token runs and whose output is added, or None."""
     hidden: int
@@ -141,6 +229,7 @@ class RoutedExpertsSpec:
     route_scale: float = 1.0
     shared: object = None
     choice_bias: bool = False
+    shared_gate: bool = False    # the shared expert's result is multiplied by sigmoid(w . h), one number a token (tensor ``shared_gate``)
 
 
 @dataclass(frozen=True)
@@ -150,6 +239,12 @@ class LayerSpec:
     output too; it may have no feed-forward (``ffn`` is None). ``kind="sandwich"``: a norm in front of and behind each
     sublayer, x += post1(mixer(norm1 x)), then x += post2(ffn(norm2 x)); with ``gated`` each sublayer's result is first
     multiplied by sigmoid(W h + b) of the sublayer's own input h (tensors ``gate1.weight``, ``gate1.bias``, ``gate2...``).
+
+    ``kind="hyper"``: hyper-connections. The model keeps ``streams`` copies of the stream; sublayer q (1 the mixer, 2 the
+    feed-forward) reads u = sum_s in_q[s] x_s, y = sublayer(norm_q(u)), and all copies change at once from the old ones:
+    x_r <- sum_s mix_q[s, r] x_s + ``residual_mult`` * out_q[r] * y (tensors ``hc1.in`` [streams], ``hc1.out`` [streams],
+    ``hc1.mix`` [streams, streams], ``hc2...``). With ``streams`` 0 there is one copy and no such tensors:
+    x <- x + ``residual_mult`` * y.
 
     ``names`` maps each part-local tensor name ("norm1.weight", "mixer.q_proj.weight",
     "ffn.down.weight", ...) to its name in the weight files."""
@@ -162,6 +257,8 @@ class LayerSpec:
     post1: NormSpec | None = None
     post2: NormSpec | None = None
     gated: bool = False
+    streams: int = 0
+    residual_mult: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -172,12 +269,14 @@ class ScheduleEntry:
     Right before the application the model may add to the stream: the embedding's output once more
     (``add_embedding``) and row ``add_row`` of the model's table of pass vectors (``ModelSpec.pass_rows``). With
     ``mix_embedding`` the stream is first replaced by W [x; x0], x0 being the embedding's output and W the model's
-    ``[width, 2 * width]`` matrix ``ModelSpec.pass_mix``."""
+    ``[width, 2 * width]`` matrix ``ModelSpec.pass_mix``. ``borrow``: a cache entry of an earlier application whose
+    keys and values this application reads beside its own entry (which still holds what it keeps for itself)."""
     layer: int
     cache: int
     add_embedding: bool = False
     add_row: int = -1
     mix_embedding: bool = False
+    borrow: int = -1
 
 
 @dataclass(frozen=True)
@@ -238,6 +337,8 @@ class ModelSpec:
     pass_rows: str | None = None  # checkpoint name of a [rows, width] table whose rows schedule entries add to the stream
     pass_rows_count: int = 0
     pass_mix: str | None = None   # checkpoint name of the [width, 2 * width] matrix of entries with ``mix_embedding``
+    streams: int = 1              # copies of the residual stream (hyper-connections): all start as the embedding's output,
+                                  # layers of kind "hyper" read and write them, their sum enters the final norm
 
     def __post_init__(self):
         seen = set()
@@ -247,6 +348,8 @@ class ModelSpec:
             seen.add(e.cache)
             if e.add_row >= 0 and not (self.pass_rows and e.add_row < self.pass_rows_count):
                 raise ValueError(f"schedule adds row {e.add_row} of a table of {self.pass_rows_count} pass vectors")
+            if e.borrow >= 0 and e.borrow == e.cache:
+                raise ValueError("a schedule entry borrows its own cache entry")
             if e.mix_embedding and not self.pass_mix:
                 raise ValueError("a schedule entry mixes the embedding into the stream and the model names no matrix for it")
         if seen and seen != set(range(len(seen))):
