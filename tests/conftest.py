@@ -75,6 +75,22 @@ def rabadra_folders(tmp_path_factory):
 
 
 @pytest.fixture(scope="session")
+def fekitar_folders(tmp_path_factory):
+    """Model folders of the tiny Fekitar configurations, float32 weights, made once per session."""
+    import torch
+
+    import tiny_fekitar
+    from sleuth_b200.weights.random_init import write_random_model
+    out = {}
+    for name, cfg in tiny_fekitar.CONFIGS.items():
+        d = tmp_path_factory.mktemp(f"fekitar_{name}")
+        write_random_model(d, cfg, seed=tiny_fekitar.SEEDS[name], dtype=torch.float32, std=tiny_fekitar.STD)
+        tiny_fekitar.sharpen(d)
+        out[name] = str(d)
+    return out
+
+
+@pytest.fixture(scope="session")
 def movalorn_folders(tmp_path_factory):
     """Model folders of the tiny Movalorn configurations, float32 weights, made once per session."""
     import torch

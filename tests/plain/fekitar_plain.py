@@ -232,15 +232,15 @@ def router_scores(h, w, p):
 
 def mixture(h, w, p, f, margins=None):
     """Softmax over all experts, the ``top`` largest chosen (lowest index first among equals), weights divided by their
-    sum; a shared expert times sigmoid(W_sg h). ``margins``: a list that receives, per token, the gap between the last
-    chosen and the first rejected score."""
+    sum; a shared expert times sigmoid(W_sg h). ``margins``: a list that receives, per token, the gap between the
+    logarithms of the last chosen and the first rejected score (the gap of their router logits)."""
     T = h.shape[0]
     E, top = f["router"]["experts"], f["router"]["top"]
     s = router_scores(h, w, p).to(h.dtype)
     order = torch.sort(s, dim=-1, descending=True, stable=True)
     idx, val = order.indices[:, :top], order.values[:, :top]
     if margins is not None:
-        margins.extend((order.values[:, top - 1] - order.values[:, top]).tolist() if top < E else [1.0] * T)
+        margins.extend((order.values[:, top - 1].log() - order.values[:, top].log()).tolist() if top < E else [1e9] * T)
     wt = val / (val.sum(dim=-1, keepdim=True) + 1e-20)
     out = torch.zeros(T, w[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(T):
