@@ -561,6 +561,37 @@ def movalorn_config(width, layers, heads, dim, rot, vdim, kv_rank, window, gru_w
             "layers": block, "loop": {"start": 1, "stop": layers, "times": 1}}
 
 
+def fekitar_config(width, layers, heads, kv_heads, dim, window, state, lin_heads, lin_dim, experts, top, ff, shared_ff, vocab=32768) -> dict:
+    """The three mixers in turn: a rotated, soft-capped attention beside a gated linear attention; a windowed attention
+    with convolutions beside a Mamba-2 recurrence; differential attention (every second one reads the keys and values of
+    the one before). Four copies of the stream; every layer has experts with a gated shared expert."""
+    rot = {"base": 10000.0, "dims": dim, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    inner = heads * dim
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff, "limit": 7.0}}
+    block, owner = [], None
+    for i in range(layers):
+        kind = i % 3
+        if kind == 0:
+            mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0, "rot": rot},
+                     "right": {"heads": lin_heads, "dim": lin_dim, "vdim": inner // lin_heads, "tau": 16.0, "rank": 16},
+                     "left_scale": 1.0, "right_scale": 1.0}
+            block.append({"type": "parallel_2", "mixer": mixer, "mlp": moe})
+        elif kind == 1:
+            mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "conv": 4, "mask": {"size": window}},
+                     "right": {"heads": heads, "vdim": dim, "state": state, "groups": 1, "conv": 4, "norm_groups": 1}}
+            block.append({"type": "parallel", "mixer": mixer, "mlp": moe})
+        else:
+            mixer = {"heads": heads // 2, "kv_heads": kv_heads // 2, "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5, "diff": 0.6, "conv": 3,
+                     "rot": {"base": 10000.0, "dims": dim}}
+            if owner is not None:
+                mixer["kv_from"], owner = owner, None
+            else:
+                owner = i
+            block.append({"type": "attention", "mixer": mixer, "mlp": moe})
+    return {"architecture": "Fekitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7, "streams": 4,
+            "layers": block}
+
+
 def qwen3_like(width, layers, heads, head_dim, inter, vocab=32768) -> dict:
     return dict(CONFIG, vocab_size=vocab, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads,
                 num_key_value_heads=max(1, heads // 2), head_dim=head_dim, intermediate_size=inter, tie_word_embeddings=False)
@@ -596,11 +627,22 @@ MOVALORN_SIZES = {
                    ff=1408, shared_ff=1408),
               dict(width=2048, layers=6, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, experts=64, top=6, ff=1408)),
 }
+# Fekitar beside Rabadra, the closest existing design (grouped-query attention over per-head keys and values, clamped-swish
+# experts with a shared expert): equal width, depth, query and key/value heads and experts. Fekitar's layers are its three
+# mixers in turn; a layer of it runs an attention AND a recurrence (or two score maps), so it does more work a layer.
+FEKITAR_SIZES = {
+    "w1024": (dict(width=1024, layers=9, heads=16, kv_heads=8, dim=64, window=1024, state=64, lin_heads=4, lin_dim=64, experts=16, top=4, ff=768,
+                   shared_ff=768),
+              dict(width=1024, layers=9, heads=16, kv_heads=8, dim=64, rot=64, experts=16, top=4, ff=768, groups=1, keep=1, shared_ff=768)),
+    "w2048": (dict(width=2048, layers=6, heads=16, kv_heads=8, dim=128, window=1024, state=128, lin_heads=8, lin_dim=128, experts=32, top=4,
+                   ff=1024, shared_ff=1024),
+              dict(width=2048, layers=6, heads=16, kv_heads=8, dim=128, rot=128, experts=32, top=4, ff=1024, groups=1, keep=1, shared_ff=1024)),
+}
 DESIGNS = {"lezepel": (lezepel_config, DESIGN_SIZES), "rabadra": (rabadra_config, RABADRA_SIZES),
-           "movalorn": (movalorn_config, MOVALORN_SIZES)}
+           "movalorn": (movalorn_config, MOVALORN_SIZES), "fekitar": (fekitar_config, FEKITAR_SIZES)}
 # the model each design stands beside, and how its configuration is made from the second entry of a size
 TWINS = {"lezepel": ("qwen3", lambda kw: qwen3_like(**kw)), "rabadra": ("qwen3", lambda kw: qwen3_like(**kw)),
-         "movalorn": ("lezepel", lambda kw: lezepel_config(**kw))}
+         "movalorn": ("lezepel", lambda kw: lezepel_config(**kw)), "fekitar": ("rabadra", lambda kw: rabadra_config(**kw))}
 
 
 def design_point(config: dict, prompt_len: int, batches, steps: int, warmup: int) -> dict:
@@ -662,8 +704,8 @@ def design_point(config: dict, prompt_len: int, batches, steps: int, warmup: int
 
 
 def run_design(args) -> dict:
-    """``--design lezepel`` / ``--design rabadra`` / ``--design movalorn``: that design beside the closest existing model
-    (the Qwen3 dense decoder for the first two, Lezepel for Movalorn) at equal width, depth and active feed-forward width,
+    """``--design lezepel`` / ``--design rabadra`` / ``--design movalorn`` / ``--design fekitar``: that design beside the closest
+    existing model (the Qwen3 dense decoder for the first two, Lezepel for Movalorn, Rabadra for Fekitar) at equal width, depth and active feed-forward width,
     random weights, bfloat16: prompt and decode throughput and where the time goes. The default workload of this file
     does not change."""
     out = {"design": args.design, "dtype": "bf16", "data": "synthetic", "prompt": args.design_prompt, "sizes": {}}
@@ -693,7 +735,7 @@ def main() -> int:
     ap.add_argument("--skip-other-configs", action="store_true",
                     help="leave out the 32-bit block and the 4B- and 8B-shaped points (a quicker run)")
     ap.add_argument("--layers5", type=int, default=0, help="layers of the 8B-shaped point (0 = all 36)")
-    ap.add_argument("--design", choices=["lezepel", "rabadra", "movalorn"], default=None,
+    ap.add_argument("--design", choices=["lezepel", "rabadra", "movalorn", "fekitar"], default=None,
                     help="instead of the default workload: this design beside the closest existing model at equal size")
     ap.add_argument("--design-size", default="all", help="one of the sizes of --design (w1024, w2048) or all")
     ap.add_argument("--design-prompt", type=int, default=2048)

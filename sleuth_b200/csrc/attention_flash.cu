@@ -57,6 +57,9 @@ struct FlashArgs {
   int pages_after_wait;         // 1: no cache page is asked for before the kernel in front has completed (see the kernel)
   const float* sinks;           // [H] or null: a learned score per head that joins the softmax denominator once,
                                 // unscaled, without a key or a value
+  // other score rules (off by default): score <- cap * tanh(score / cap), then score -= slopes[head] * (query position - key position)
+  float softcap_log2;           // cap * log2(e), or 0
+  const float* slopes;          // [H] or null
 };
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -144,12 +147,14 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
   }
   // positions of this thread's two rows (g and g + 8 of the warp's 16)
   int pos_r[2], lo_r[2];
+  float slope_r[2];             // in log2 units, like the scores
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int R = r0 + warp * 16 + g + 8 * h;
     const int p = R < rows_total ? past + R / G : -1;      // -1: a padding row sees nothing
     pos_r[h] = p;
     lo_r[h] = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    slope_r[h] = a.slopes != nullptr && R < rows_total ? a.slopes[kh * G + R % G] * kLog2e : 0.0f;
   }
   const int warp_p_min = past + min(rows_total - 1, r0 + warp * 16) / G;
   const int warp_R_last = min(rows_total - 1, r0 + warp * 16 + 15);
@@ -199,6 +204,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
         for (int e = 0; e < 4; ++e) {
           const int h = e >> 1;
           float v = s[j][e] * a.scale_log2;
+          if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanhf(v / a.softcap_log2);
+          if (a.slopes != nullptr) v -= slope_r[h] * (float)(pos_r[h] - (key0 + j * 8 + 2 * t4 + (e & 1)));
           if (need_mask) {
             const int key = key0 + j * 8 + 2 * t4 + (e & 1);
             if (key > pos_r[h] || key < lo_r[h]) v = -INFINITY;
@@ -366,6 +373,9 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
   const int* table = a.block_table + (size_t)seq * a.table_stride;
   const int head0 = kh * G + rt * 16;          // first query head of this row tile
   const int rows = min(16, G - rt * 16);
+  float slope_r[2];                            // this thread's two rows (heads head0 + g and head0 + g + 8), log2 units
+#pragma unroll
+  for (int h = 0; h < 2; ++h) slope_r[h] = a.slopes != nullptr && g + 8 * h < rows ? a.slopes[head0 + g + 8 * h] * kLog2e : 0.0f;
   // this slice's page numbers, fetched once so that the page loop does not wait for the table
   __shared__ int my_pages[kFlashThreads];
   __shared__ int ticket;
@@ -490,6 +500,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
           for (int e = 0; e < 4; ++e) {
             const int key = key0 + j * 8 + 2 * t4 + (e & 1);
             float v = s[j][e] * a.scale_log2;
+            if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanhf(v / a.softcap_log2);
+            if (a.slopes != nullptr) v -= slope_r[e >> 1] * (float)(pos - key);
             if (key > pos || key < key_lo) v = -INFINITY;
             s[j][e] = v;
           }
@@ -706,10 +718,10 @@ extern "C" long long slb_attention_decode_scratch_floats(int n_seqs, int heads, 
   return splits <= 1 ? 0 : (long long)n_seqs * heads * splits * (head_dim + 2);
 }
 
-extern "C" int slb_attention_prefill(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                     const int* seq_start, const int* past, const int* counts, const int* block_table,
-                                     int table_stride, int n_seqs, int max_count, int heads, int kv_heads, int head_dim,
-                                     int window, float scale, const float* sinks, void* stream) {
+static int attention_prefill_any(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                 const int* seq_start, const int* past, const int* counts, const int* block_table,
+                                 int table_stride, int n_seqs, int max_count, int heads, int kv_heads, int head_dim,
+                                 int window, float scale, const float* sinks, const float* slopes, float softcap, void* stream) {
   SLB_REQUIRE(n_seqs >= 0 && max_count >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention (prefill): seqs=%d max_count=%d heads=%d kv_heads=%d", n_seqs, max_count, heads, kv_heads);
   SLB_REQUIRE(head_dim == 64 || head_dim == 128, "attention (prefill): the tensor-core kernel takes head_dim 64 or 128, got %d", head_dim);
@@ -720,18 +732,36 @@ extern "C" int slb_attention_prefill(const void* q, const void* k_pool, const vo
   a.out = (__nv_bfloat16*)out; a.seq_start = seq_start; a.past = past; a.counts = counts;
   a.block_table = block_table; a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads;
   a.window = window; a.scale_log2 = scale * 1.4426950408889634f; a.splits = 1; a.sinks = sinks;
+  a.slopes = slopes; a.softcap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   return head_dim == 64 ? launch_prefill<64>(a, n_seqs, max_count, (cudaStream_t)stream)
                         : launch_prefill<128>(a, n_seqs, max_count, (cudaStream_t)stream);
 }
 
-extern "C" int slb_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                    const int* seq_start, const int* past, const int* block_table, int table_stride,
-                                    int n_seqs, int heads, int kv_heads, int head_dim, int window, float scale,
-                                    int splits, float* scratch, long long scratch_floats, int* counters,
-                                    long long n_counters, const void* qkv, int qkv_kv_heads, const float* bias,
-                                    const float* q_gain, const float* k_gain, const float* cos_table,
-                                    const float* sin_table, float eps, const void* next, long long next_bytes,
-                                    const float* sinks, void* stream) {
+extern "C" int slb_attention_prefill(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                     const int* seq_start, const int* past, const int* counts, const int* block_table,
+                                     int table_stride, int n_seqs, int max_count, int heads, int kv_heads, int head_dim,
+                                     int window, float scale, const float* sinks, void* stream) {
+  return attention_prefill_any(q, k_pool, v_pool, out, seq_start, past, counts, block_table, table_stride, n_seqs, max_count, heads,
+                               kv_heads, head_dim, window, scale, sinks, nullptr, 0.0f, stream);
+}
+
+// The same kernel with a distance penalty per head (`slopes` [heads] or null) and a soft cap (0 = none) on the scores.
+extern "C" int slb_attention_prefill_scored(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                            const int* seq_start, const int* past, const int* counts, const int* block_table,
+                                            int table_stride, int n_seqs, int max_count, int heads, int kv_heads, int head_dim,
+                                            int window, float scale, const float* slopes, float softcap, void* stream) {
+  return attention_prefill_any(q, k_pool, v_pool, out, seq_start, past, counts, block_table, table_stride, n_seqs, max_count, heads,
+                               kv_heads, head_dim, window, scale, nullptr, slopes, softcap, stream);
+}
+
+static int attention_decode_any(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                const int* seq_start, const int* past, const int* block_table, int table_stride,
+                                int n_seqs, int heads, int kv_heads, int head_dim, int window, float scale,
+                                int splits, float* scratch, long long scratch_floats, int* counters,
+                                long long n_counters, const void* qkv, int qkv_kv_heads, const float* bias,
+                                const float* q_gain, const float* k_gain, const float* cos_table,
+                                const float* sin_table, float eps, const void* next, long long next_bytes,
+                                const float* sinks, const float* slopes, float softcap, void* stream) {
   // qkv != null: `q` is ignored; the kernel takes the new token's raw projection rows [n, (H + 2 * qkv_kv_heads) * hd],
   // applies bias, QK-norm and the rotation itself, and (qkv_kv_heads == kv_heads) writes the token's key and value
   // into the cache. cos/sin tables, if given, are [positions, hd / 2]: the whole head rotates.
@@ -762,9 +792,35 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
   a.part_ml = scratch ? scratch + (size_t)n_seqs * heads * splits * head_dim : nullptr;
   a.qkv = (const __nv_bfloat16*)qkv; a.qkv_kv_heads = qkv_kv_heads; a.bias = bias; a.q_gain = q_gain; a.k_gain = k_gain;
   a.cos_table = cos_table; a.sin_table = sin_table; a.eps = eps; a.sinks = sinks;
+  a.slopes = slopes; a.softcap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   a.pages_after_wait = (qkv == nullptr || qkv_kv_heads == 0 || pdl_mode() == 1) ? 1 : 0;
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "attention (decode): the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
   return head_dim == 64 ? launch_decode<64>(a, n_seqs, (cudaStream_t)stream)
                         : launch_decode<128>(a, n_seqs, (cudaStream_t)stream);
+}
+
+extern "C" int slb_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                    const int* seq_start, const int* past, const int* block_table, int table_stride,
+                                    int n_seqs, int heads, int kv_heads, int head_dim, int window, float scale,
+                                    int splits, float* scratch, long long scratch_floats, int* counters,
+                                    long long n_counters, const void* qkv, int qkv_kv_heads, const float* bias,
+                                    const float* q_gain, const float* k_gain, const float* cos_table,
+                                    const float* sin_table, float eps, const void* next, long long next_bytes,
+                                    const float* sinks, void* stream) {
+  return attention_decode_any(q, k_pool, v_pool, out, seq_start, past, block_table, table_stride, n_seqs, heads, kv_heads, head_dim,
+                              window, scale, splits, scratch, scratch_floats, counters, n_counters, qkv, qkv_kv_heads, bias, q_gain,
+                              k_gain, cos_table, sin_table, eps, next, next_bytes, sinks, nullptr, 0.0f, stream);
+}
+
+// One token a sequence with post-processed queries, a distance penalty per head (`slopes` or null) and a soft cap (0 = none).
+extern "C" int slb_attention_decode_scored(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                           const int* seq_start, const int* past, const int* block_table, int table_stride,
+                                           int n_seqs, int heads, int kv_heads, int head_dim, int window, float scale,
+                                           int splits, float* scratch, long long scratch_floats, int* counters,
+                                           long long n_counters, const void* next, long long next_bytes, const float* slopes,
+                                           float softcap, void* stream) {
+  return attention_decode_any(q, k_pool, v_pool, out, seq_start, past, block_table, table_stride, n_seqs, heads, kv_heads, head_dim,
+                              window, scale, splits, scratch, scratch_floats, counters, n_counters, nullptr, 0, nullptr, nullptr,
+                              nullptr, nullptr, nullptr, 0.0f, next, next_bytes, nullptr, slopes, softcap, stream);
 }

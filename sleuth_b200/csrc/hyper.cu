@@ -7,6 +7,7 @@
 //   streams_sum_kernel    x = sum_s x_s
 //   pair_combine_kernel   target (=|+=) 0.5 * (a / rms(a) * ga + b / rms(b) * gb), or sa * a + sb * b without gains
 //   row_gate_kernel       target (=|+=) sigmoid(h . w) * y, one gate value a token
+//   sigmoid_gate_kernel   y <- y * sigmoid(gate), element by element, in place
 #include <math.h>
 
 #include "common.cuh"
@@ -138,6 +139,17 @@ __global__ void __launch_bounds__(256) row_gate_kernel(const T* __restrict__ h, 
   for (int c = threadIdx.x; c < d; c += blockDim.x) o[c] = accumulate ? fmaf(g, yr[c], o[c]) : g * yr[c];
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256) sigmoid_gate_kernel(T* __restrict__ y, const float* __restrict__ gate, long long gate_stride,
+                                                           long long rows, int C) {
+  pdl_enter();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * C) return;
+  const long long t = i / C;
+  const int c = (int)(i - t * C);
+  y[i] = from_f32<T>(to_f32(y[i]) / (1.0f + expf(-gate[(size_t)t * gate_stride + c])));
+}
+
 }  // namespace slb
 
 using namespace slb;
@@ -196,4 +208,14 @@ extern "C" int slb_row_gate(const void* h, const float* w, const float* y, float
   else if (dtype == kBF16) launch(row_gate_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(256), 0, s, (const __nv_bfloat16*)h, w, y, target, k, d, accumulate);
   else return fail(1, "row_gate: unknown dtype %d", dtype);
   return check_launch("row_gate");
+}
+
+extern "C" int slb_sigmoid_gate(void* y, const float* gate, long long gate_stride, long long rows, int C, int dtype, void* stream) {
+  SLB_REQUIRE(rows >= 0 && C > 0 && gate_stride >= C, "sigmoid_gate: rows=%lld channels=%d", rows, C);
+  if (rows == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kF32) launch(sigmoid_gate_kernel<float>, per_element(rows * C), dim3(256), 0, s, (float*)y, gate, gate_stride, rows, C);
+  else if (dtype == kBF16) launch(sigmoid_gate_kernel<__nv_bfloat16>, per_element(rows * C), dim3(256), 0, s, (__nv_bfloat16*)y, gate, gate_stride, rows, C);
+  else return fail(1, "sigmoid_gate: unknown dtype %d", dtype);
+  return check_launch("sigmoid_gate");
 }

@@ -78,6 +78,12 @@ struct ScanArgs {
   int n_seqs, heads, groups, N, P;
   int a_per_channel;                   // 1: a is [tokens, heads * N]; 0: [tokens, heads]
   float q_scale;
+  // Long portions in chunks (chunk_len > 0): every sequence's tokens of the step are cut into `chunks` chunks of chunk_len
+  // tokens (the last ones may be short or empty). mode 1 walks each chunk from a zero state and leaves its end state in
+  // `starts` [n_seqs, chunks, heads, N, P]; scan_starts_kernel then turns those into the chunks' true start states and
+  // updates the sequences' states; mode 2 walks each chunk from its start state and writes the outputs.
+  int chunk_len, chunks, mode;
+  float* starts;
 };
 
 // One thread per (sequence, head, value channel p) keeps column p of the head's state, N values, in registers and walks
@@ -88,18 +94,26 @@ template <int NB>
 __global__ void __launch_bounds__(128) decay_scan_kernel(ScanArgs a) {
   pdl_enter();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long total = (long long)a.n_seqs * a.heads * a.P;
+  const int pieces = a.mode == 0 ? 1 : a.chunks;
+  const long long total = (long long)a.n_seqs * pieces * a.heads * a.P;
   if (i >= total) return;
   const int p = (int)(i % a.P);
   const int h = (int)((i / a.P) % a.heads);
-  const int seq = (int)(i / ((long long)a.P * a.heads));
+  const int piece = (int)((i / ((long long)a.P * a.heads)) % pieces);
+  const int seq = (int)(i / ((long long)a.P * a.heads * pieces));
   const int g = h / (a.heads / a.groups);
   const int N = a.N;
+  int t0 = a.seq_start[seq], t1 = a.seq_start[seq + 1];
   float* st = a.state + (((size_t)a.slots[seq] * a.heads + h) * N) * a.P + p;
+  if (a.mode != 0) {
+    t0 += piece * a.chunk_len;
+    t1 = min(t1, t0 + a.chunk_len);
+    if (t0 >= t1) return;                       // a chunk beyond the sequence's tokens
+    st = a.starts + ((((size_t)seq * a.chunks + piece) * a.heads + h) * N) * a.P + p;
+  }
   float S[NB];
 #pragma unroll
-  for (int n = 0; n < NB; ++n) S[n] = n < N ? st[(size_t)n * a.P] : 0.0f;
-  const int t0 = a.seq_start[seq], t1 = a.seq_start[seq + 1];
+  for (int n = 0; n < NB; ++n) S[n] = (n < N && a.mode != 1) ? st[(size_t)n * a.P] : 0.0f;
   for (int t = t0; t < t1; ++t) {
     const float* qr = a.q + (size_t)t * a.q_stride + (size_t)g * N;
     const float* kr = a.k + (size_t)t * a.k_stride + (size_t)g * N;
@@ -116,11 +130,51 @@ __global__ void __launch_bounds__(128) decay_scan_kernel(ScanArgs a) {
         o = fmaf(S[n], qr[n], o);
       }
     }
-    a.out[(size_t)t * ((size_t)a.heads * a.P) + (size_t)h * a.P + p] = o * a.q_scale;
+    if (a.mode != 1) a.out[(size_t)t * ((size_t)a.heads * a.P) + (size_t)h * a.P + p] = o * a.q_scale;
   }
+  if (a.mode == 2) return;
 #pragma unroll
   for (int n = 0; n < NB; ++n)
     if (n < N) st[(size_t)n * a.P] = S[n];
+}
+
+// The product of a chunk's decays: one thread per (sequence, chunk, head, key channel or 0). prod: [n_seqs, chunks, heads, Nn].
+__global__ void __launch_bounds__(256) scan_decay_kernel(ScanArgs a, float* __restrict__ prod) {
+  pdl_enter();
+  const int Nn = a.a_per_channel ? a.N : 1;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)a.n_seqs * a.chunks * a.heads * Nn) return;
+  const int n = (int)(i % Nn);
+  const int h = (int)((i / Nn) % a.heads);
+  const int piece = (int)((i / ((long long)Nn * a.heads)) % a.chunks);
+  const int seq = (int)(i / ((long long)Nn * a.heads * a.chunks));
+  const int t0 = a.seq_start[seq] + piece * a.chunk_len, t1 = min(a.seq_start[seq + 1], t0 + a.chunk_len);
+  float v = 1.0f;
+  for (int t = t0; t < t1; ++t) v *= a.a[(size_t)t * a.a_stride + (a.a_per_channel ? (size_t)h * a.N + n : (size_t)h)];
+  prod[i] = v;
+}
+
+// One thread per (sequence, head, n, p) walks the chunks in order: a chunk's end state (from zero) is replaced by its true
+// start state, and the state after the last chunk goes back to the sequence's slot.
+__global__ void __launch_bounds__(256) scan_starts_kernel(ScanArgs a, const float* __restrict__ prod) {
+  pdl_enter();
+  const int Nn = a.a_per_channel ? a.N : 1;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long per_seq = (long long)a.heads * a.N * a.P;
+  if (i >= (long long)a.n_seqs * per_seq) return;
+  const int seq = (int)(i / per_seq);
+  const long long r = i - (long long)seq * per_seq;          // (h, n, p)
+  const int h = (int)(r / ((long long)a.N * a.P)), n = (int)((r / a.P) % a.N);
+  const int count = a.seq_start[seq + 1] - a.seq_start[seq];
+  float* st = a.state + (size_t)a.slots[seq] * per_seq + r;
+  float s = *st;
+  for (int c = 0; c < a.chunks && c * a.chunk_len < count; ++c) {
+    float* e = a.starts + ((size_t)seq * a.chunks + c) * per_seq + r;
+    const float end = *e;
+    *e = s;
+    s = fmaf(prod[(((size_t)seq * a.chunks + c) * a.heads + h) * Nn + (a.a_per_channel ? n : 0)], s, end);
+  }
+  *st = s;
 }
 
 // raw: [tokens, raw_stride] (the step sizes' pre-activations of head h at raw[t * raw_stride + h]).
@@ -214,24 +268,65 @@ extern "C" int slb_causal_conv(const float* in, long long in_stride, const float
   return check_launch("conv_state");
 }
 
+static void launch_scan(const ScanArgs& g, cudaStream_t s) {
+  const long long total = (long long)g.n_seqs * (g.mode == 0 ? 1 : g.chunks) * g.heads * g.P;
+  const dim3 grid((unsigned)((total + 127) / 128)), block(128);
+  if (g.N <= 16) launch(decay_scan_kernel<16>, grid, block, 0, s, g);
+  else if (g.N <= 32) launch(decay_scan_kernel<32>, grid, block, 0, s, g);
+  else if (g.N <= 64) launch(decay_scan_kernel<64>, grid, block, 0, s, g);
+  else if (g.N <= 128) launch(decay_scan_kernel<128>, grid, block, 0, s, g);
+  else launch(decay_scan_kernel<256>, grid, block, 0, s, g);
+}
+
+// Portions of more than kScanWhole tokens run in chunks (three passes); the chunk length grows with the portion so that
+// the middle pass, which walks the chunks one after another, stays short.
+constexpr int kScanWhole = 48;
+static int scan_chunk_len(int max_count) { return max_count <= 4096 ? 32 : 128; }
+
+// Floats of scratch memory that a step whose longest portion has max_count tokens needs (0: it runs in one pass).
+extern "C" long long slb_decay_scan_scratch_floats(int n_seqs, int max_count, int heads, int N, int P, int a_per_channel) {
+  if (max_count <= kScanWhole) return 0;
+  const long long chunks = (max_count + scan_chunk_len(max_count) - 1) / scan_chunk_len(max_count);
+  return (long long)n_seqs * chunks * heads * ((long long)N * P + (a_per_channel ? N : 1));
+}
+
 extern "C" int slb_decay_scan(const float* q, long long q_stride, const float* k, long long k_stride, const float* v,
                               long long v_stride, const float* a, long long a_stride, int a_per_channel, const float* vs,
                               long long vs_stride, float* state, const int* slots, const int* seq_start, float* out,
-                              int n_seqs, int heads, int groups, int N, int P, float q_scale, void* stream) {
+                              int n_seqs, int heads, int groups, int N, int P, float q_scale, int max_count, float* scratch,
+                              long long scratch_floats, void* stream) {
   SLB_REQUIRE(n_seqs >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && N > 0 && N <= 256 && P > 0,
               "decay_scan: heads=%d groups=%d state rows=%d (at most 256) columns=%d", heads, groups, N, P);
   if (n_seqs == 0) return 0;
   ScanArgs g{q, k, v, a, vs, q_stride, k_stride, v_stride, a_stride, vs_stride, state, slots, seq_start, out,
-             n_seqs, heads, groups, N, P, a_per_channel, q_scale};
+             n_seqs, heads, groups, N, P, a_per_channel, q_scale, 0, 1, 0, nullptr};
   cudaStream_t s = (cudaStream_t)stream;
-  const long long total = (long long)n_seqs * heads * P;
-  const dim3 grid((unsigned)((total + 127) / 128)), block(128);
-  if (N <= 16) launch(decay_scan_kernel<16>, grid, block, 0, s, g);
-  else if (N <= 32) launch(decay_scan_kernel<32>, grid, block, 0, s, g);
-  else if (N <= 64) launch(decay_scan_kernel<64>, grid, block, 0, s, g);
-  else if (N <= 128) launch(decay_scan_kernel<128>, grid, block, 0, s, g);
-  else launch(decay_scan_kernel<256>, grid, block, 0, s, g);
-  return check_launch("decay_scan");
+  const long long need = slb_decay_scan_scratch_floats(n_seqs, max_count, heads, N, P, a_per_channel);
+  if (need == 0) {
+    launch_scan(g, s);
+    return check_launch("decay_scan");
+  }
+  SLB_REQUIRE(scratch != nullptr && scratch_floats >= need, "decay_scan: %lld floats of scratch memory are needed, %lld were given",
+              need, scratch_floats);
+  g.chunk_len = scan_chunk_len(max_count);
+  g.chunks = (max_count + g.chunk_len - 1) / g.chunk_len;
+  g.starts = scratch;
+  float* prod = scratch + (size_t)n_seqs * g.chunks * heads * N * P;
+  g.mode = 1;
+  launch_scan(g, s);
+  int rc = check_launch("decay_scan (chunks from zero)");
+  if (rc) return rc;
+  const long long np = (long long)n_seqs * g.chunks * heads * (a_per_channel ? N : 1);
+  launch(scan_decay_kernel, dim3((unsigned)((np + 255) / 256)), dim3(256), 0, s, g, prod);
+  rc = check_launch("decay_scan (decay products)");
+  if (rc) return rc;
+  const long long ns = (long long)n_seqs * heads * N * P;
+  launch(scan_starts_kernel, dim3((unsigned)((ns + 255) / 256)), dim3(256), 0, s, g, (const float*)prod);
+  rc = check_launch("decay_scan (chunk starts)");
+  if (rc) return rc;
+  g.mode = 2;
+  launch_scan(g, s);
+  return check_launch("decay_scan (chunks from their starts)");
 }
 
 extern "C" int slb_step_decay(const float* raw, long long raw_stride, const float* dt_bias, const float* a_log, float* dt,

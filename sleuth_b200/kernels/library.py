@@ -171,8 +171,11 @@ _SIGNATURES = {
     "slb_gemm_tc_gated": [P, P, P, I, I, I, I, I, F, F, P, P],
     "slb_moe_experts": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
     "slb_attention_scored": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, F, I, I, P, L, I, I, P],
+    "slb_attention_prefill_scored": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, F, P],
+    "slb_attention_decode_scored": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P, L, P, L, P, F, P],
+    "slb_sigmoid_gate": [P, P, L, I, I, I, P],
     "slb_causal_conv": [P, L, P, P, P, P, P, P, P, L, I, I, I, I, I, P],
-    "slb_decay_scan": [P, L, P, L, P, L, P, L, I, P, L, P, P, P, P, I, I, I, I, I, F, P],
+    "slb_decay_scan": [P, L, P, L, P, L, P, L, I, P, L, P, P, P, P, I, I, I, I, I, F, I, P, L, P],
     "slb_step_decay": [P, L, P, P, P, P, I, I, P],
     "slb_channel_decay": [P, P, I, I, F, P],
     "slb_gated_group_norm": [P, P, L, P, I, P, L, P, I, P, I, I, I, I, F, I, P],

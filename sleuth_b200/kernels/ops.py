@@ -350,19 +350,32 @@ def _sinks_ok(sinks, heads: int) -> None:
 
 
 def attention_prefill(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
-                      kv_heads: int, head_dim: int, window: int, scale: float, stream=None, sinks=None) -> None:
+                      kv_heads: int, head_dim: int, window: int, scale: float, stream=None, sinks=None, slopes=None,
+                      softcap: float = 0.0) -> None:
     """Tensor-core attention for a step in which sequences bring any number of tokens. ``sinks`` [heads]: a learned
-    score per head in the softmax denominator (as in ``attention``)."""
-    _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table)
+    score per head in the softmax denominator (as in ``attention``). ``slopes`` [heads] float32 / ``softcap``: the score
+    rules of ``attention_scored`` (not together with sinks)."""
+    _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table, slopes)
     _sinks_ok(sinks, heads)
+    _slopes_ok(slopes, heads, sinks)
     T, n = q.shape[0], block_table.shape[0]
     _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
     _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tensor cores): bfloat16 only")
     _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
     _need(seq_start.numel() >= n + 1 and past.numel() >= n and counts.numel() >= n, "attention: per-sequence tables")
+    if slopes is not None or softcap:
+        lib().call("slb_attention_prefill_scored", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
+                   _p(block_table), block_table.shape[1], n, int(max_count), heads, kv_heads, head_dim, int(window),
+                   float(scale), _p(slopes), float(softcap), stream if stream is not None else current_stream())
+        return
     lib().call("slb_attention_prefill", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
                _p(block_table), block_table.shape[1], n, int(max_count), heads, kv_heads, head_dim, int(window),
                float(scale), _p(sinks), stream if stream is not None else current_stream())
+
+
+def _slopes_ok(slopes, heads: int, sinks) -> None:
+    _need(slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == heads and sinks is None),
+          "attention: slopes are float32, one per head, and do not go with sinks")
 
 
 def attention_tc_supported(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
@@ -407,16 +420,19 @@ def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, m
 def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads: int, kv_heads: int, head_dim: int,
                      window: int, scale: float, splits: int, scratch, stream=None, qkv=None, qkv_kv_heads: int = 0,
                      bias=None, q_gain=None, k_gain=None, cos=None, sin=None, eps: float = 1e-6, next_read=None,
-                     sinks=None) -> None:
+                     sinks=None, slopes=None, softcap: float = 0.0) -> None:
     """Tensor-core attention for a step in which every sequence brings one token (split-KV).
 
     With ``qkv`` (the raw fused projection ``[n, (heads + 2 * qkv_kv_heads) * head_dim]``) the kernel also does what
     ``qkv_post`` does for that token: bias, per-head QK-norm, rotation of the whole head, and, when
     ``qkv_kv_heads == kv_heads``, the write of its key and value into the cache; ``q`` is then not read.
     ``next_read``: a tensor that the kernel after this one reads and no kernel writes (a weight matrix); the blocks
-    ask the L2 cache for it once their own pages are on their way."""
-    _cuda(q, k_pool, v_pool, out, seq_start, past, block_table, scratch, qkv, bias, q_gain, k_gain, cos, sin)
+    ask the L2 cache for it once their own pages are on their way. ``slopes`` / ``softcap``: the score rules of
+    ``attention_scored``, with post-processed queries only."""
+    _cuda(q, k_pool, v_pool, out, seq_start, past, block_table, scratch, qkv, bias, q_gain, k_gain, cos, sin, slopes)
     _sinks_ok(sinks, heads)
+    _slopes_ok(slopes, heads, sinks)
+    _need(not (slopes is not None or softcap) or qkv is None, "attention (decode): other score rules go with post-processed queries")
     n = block_table.shape[0]
     _need(out.shape == (n, heads * head_dim) and out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16,
           "attention (tensor cores): shapes disagree or not bfloat16")
@@ -430,6 +446,13 @@ def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads
             _need(v is None or v.dtype == torch.float32, "attention: gains, biases and tables are float32")
         _need(cos is None or (cos.shape[1] == head_dim // 2 and sin.shape == cos.shape), "attention: rotation tables")
     counters = _decode_counters(out.device, n * kv_heads * ((heads // kv_heads + 15) // 16)) if splits > 1 else None
+    if slopes is not None or softcap:
+        lib().call("slb_attention_decode_scored", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past),
+                   _p(block_table), block_table.shape[1], n, heads, kv_heads, head_dim, int(window), float(scale),
+                   int(splits), _p(scratch), 0 if scratch is None else scratch.numel(), _p(counters),
+                   0 if counters is None else counters.numel(), _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read),
+                   _p(slopes), float(softcap), stream if stream is not None else current_stream())
+        return
     lib().call("slb_attention_decode", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past),
                _p(block_table), block_table.shape[1], n, heads, kv_heads, head_dim, int(window), float(scale),
                int(splits), _p(scratch), 0 if scratch is None else scratch.numel(), _p(counters),
@@ -1113,13 +1136,22 @@ def causal_conv(u, weight, bias, state, slots, tok_seq, seq_start, out, act: boo
                T, slots.numel(), C, taps, 1 if act else 0, _st(stream))
 
 
+def decay_scan_scratch_floats(n_seqs: int, max_count: int, heads: int, N: int, P: int, per_channel: bool) -> int:
+    """Scratch floats ``decay_scan`` needs for a step whose longest portion has ``max_count`` tokens (0: one pass)."""
+    fn = lib().dll.slb_decay_scan_scratch_floats
+    fn.argtypes, fn.restype = [ctypes.c_int] * 6, ctypes.c_longlong
+    return int(fn(int(n_seqs), int(max_count), int(heads), int(N), int(P), 1 if per_channel else 0))
+
+
 def decay_scan(q, k, v, a, state, slots, seq_start, out, heads: int, groups: int, per_channel: bool, v_scale=None,
-               q_scale: float = 1.0, stream=None) -> None:
+               q_scale: float = 1.0, stream=None, max_count: int = 1, scratch=None) -> None:
     """Per head S_t = diag(a_t) S_(t-1) + k_t v_t^T and out_t = S_t^T q_t * ``q_scale`` over each sequence's tokens of the
     step, from and back into ``state`` float32 [slots, heads, N, P]. q, k: float32 rows of groups * N values (head h reads
     group h // (heads / groups)); v: rows of heads * P values, times ``v_scale`` [T, heads] when given; a: rows of
-    heads * N decays (``per_channel``) or of one decay a head. out: float32 [T, heads * P]."""
-    _cuda(state, slots, seq_start, out)
+    heads * N decays (``per_channel``) or of one decay a head. out: float32 [T, heads * P]. ``max_count``: the longest
+    portion of the step; long portions run in chunks (each from a zero state, then the chunks' start states in order, then
+    each from its start state) and need ``scratch`` (``decay_scan_scratch_floats``)."""
+    _cuda(state, slots, seq_start, out, scratch)
     _, H, N, P = state.shape
     T = out.shape[0]
     _need(H == heads and heads % groups == 0 and state.dtype == torch.float32 and out.dtype == torch.float32
@@ -1129,8 +1161,10 @@ def decay_scan(q, k, v, a, state, slots, seq_start, out, heads: int, groups: int
     as_ = _rows_f32(a, heads * N if per_channel else heads, "decay_scan a")
     ss = _rows_f32(v_scale, heads, "decay_scan v_scale") if v_scale is not None else 0
     _need(slots.dtype == torch.int32 and seq_start.dtype == torch.int32 and seq_start.numel() >= slots.numel() + 1, "decay_scan: tables")
+    _need(scratch is None or scratch.dtype == torch.float32, "decay_scan: scratch is float32")
     lib().call("slb_decay_scan", _p(q), qs, _p(k), ks, _p(v), vs_, _p(a), as_, 1 if per_channel else 0, _p(v_scale), ss, _p(state),
-               _p(slots), _p(seq_start), _p(out), slots.numel(), heads, groups, N, P, float(q_scale), _st(stream))
+               _p(slots), _p(seq_start), _p(out), slots.numel(), heads, groups, N, P, float(q_scale), int(max_count), _p(scratch),
+               0 if scratch is None else scratch.numel(), _st(stream))
 
 
 def step_decay(raw, dt_bias, a_log, dt, decay, stream=None) -> None:
@@ -1262,3 +1296,12 @@ def row_gate(h, w, y, target, accumulate: bool = True, stream=None) -> None:
     _need(h.dtype in DT and w.dtype == torch.float32 and w.numel() == k and y.dtype == target.dtype == torch.float32
           and y.shape == target.shape == (T, d), "row_gate: shapes")
     lib().call("slb_row_gate", _p(h), _p(w), _p(y), _p(target), T, k, d, 1 if accumulate else 0, DT[h.dtype], _st(stream))
+
+
+def sigmoid_gate(y, gate, stream=None) -> None:
+    """y[t, c] <- y[t, c] * sigmoid(gate[t, c]) in place; y [T, C] in the run dtype, gate float32 rows of at least C values."""
+    _cuda(y)
+    T, C = y.shape
+    gs = _rows_f32(gate, C, "sigmoid_gate")
+    _need(y.dtype in DT and gate.shape[0] == T, "sigmoid_gate: shapes")
+    lib().call("slb_sigmoid_gate", _p(y), _p(gate), gs, T, C, DT[y.dtype], _st(stream))

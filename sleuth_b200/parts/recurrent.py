@@ -133,8 +133,10 @@ class StateSpace(Part):
         dt, decay = ws.take((T, s.heads), torch.float32), ws.take((T, s.heads), torch.float32)
         ops.step_decay(p[:, 2 * inner + 2 * bc:], self.dt_bias, self.a_log, dt, decay, b.stream)
         y = ws.take((T, inner), torch.float32)
+        need = ops.decay_scan_scratch_floats(b.n, b.max_count, s.heads, s.state, s.value_dim, False)
+        scratch = ws.take((need,), torch.float32) if need else None
         ops.decay_scan(xbc[:, inner + bc:], xbc[:, inner:inner + bc], xbc[:, :inner], decay, view["state"].state, b.slots,
-                       b.seq_start, y, s.heads, s.groups, False, v_scale=dt, stream=b.stream)
+                       b.seq_start, y, s.heads, s.groups, False, v_scale=dt, stream=b.stream, max_count=b.max_count, scratch=scratch)
         g = ws.take((T, inner), self.ctx.dtype)
         ops.gated_group_norm(y, p[:, :inner], self.gain, g, s.norm_groups, s.eps, True, skip=xbc[:, :inner], skip_gain=self.skip,
                              head_width=s.value_dim, stream=b.stream)
@@ -187,8 +189,10 @@ class GatedLinearAttention(Part):
         z = self.a2.forward(low, ws=ws, stream=b.stream, out_dtype=torch.float32)
         ops.channel_decay(z, self.a2_bias, s.tau, b.stream)
         y = ws.take((T, nv), torch.float32)
+        need = ops.decay_scan_scratch_floats(b.n, b.max_count, s.heads, s.head_dim, s.value_dim, True)
+        scratch = ws.take((need,), torch.float32) if need else None
         ops.decay_scan(p[:, :nk], p[:, nk:2 * nk], p[:, 2 * nk:2 * nk + nv], z, view["state"].state, b.slots, b.seq_start, y,
-                       s.heads, s.heads, True, q_scale=s.head_dim ** -0.5, stream=b.stream)
+                       s.heads, s.heads, True, q_scale=s.head_dim ** -0.5, stream=b.stream, max_count=b.max_count, scratch=scratch)
         g = ws.take((T, nv), self.ctx.dtype)
         ops.gated_group_norm(y, p[:, 2 * nk + nv:2 * nk + 2 * nv], self.gain, g, s.heads, s.eps, False, stream=b.stream)
         self.o.forward(g, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None), **result_target(b, x))

@@ -54,6 +54,9 @@ class ScoredAttention(Part):
                                        dtype=torch.float32, device=ctx.device)
         self.qkvg = self.o = self.conv = self.q_gain = self.k_gain = None
         self.lam = 0.0
+        # one map, bfloat16, keys and values of one width that the tensor-core kernels take: prompts and single tokens run
+        # on the mma.sync kernels (which know the soft cap and the distance penalty); everything else on the general kernel
+        self.flash = s.maps == 1 and s.value_dim == s.head_dim and ops.flash_supported(s.head_dim, ctx.dtype)
 
     def _proj(self):
         return ["q"] if self.spec.reads_shared_kv else ["q", "k", "v"]
@@ -128,7 +131,20 @@ class ScoredAttention(Part):
                       self.position.rot_dim, s.eps, b.stream)
         gate = p[:, nqkv:] if self.ng else None
         y = ws.take((T, s.heads * s.value_dim), dt)
-        if s.maps == 1:
+        if self.flash:
+            if b.max_count == 1:
+                splits = ops.decode_splits(b.n, s.kv_heads, s.heads // s.kv_heads, table.shape[1])
+                floats = ops.decode_scratch_floats(b.n, s.heads, s.head_dim, splits)
+                scratch = ws.take((floats,), torch.float32) if floats else None
+                ops.attention_decode(q, kv.k_pool, kv.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads, s.head_dim,
+                                     kv.window, self.scale, splits, scratch, b.stream, next_read=self.o.weight, slopes=self.slopes,
+                                     softcap=s.softcap)
+            else:
+                ops.attention_prefill(q, kv.k_pool, kv.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count, s.heads,
+                                      s.kv_heads, s.head_dim, kv.window, self.scale, b.stream, slopes=self.slopes, softcap=s.softcap)
+            if gate is not None:
+                ops.sigmoid_gate(y, gate, b.stream)
+        elif s.maps == 1:
             ops.attention_scored(q, kv.k_pool, kv.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads, s.head_dim,
                                  kv.window, self.scale, b.stream, slopes=self.slopes, softcap=s.softcap, gate=gate,
                                  value_dim=s.value_dim)

@@ -97,6 +97,18 @@ def distance_slopes(H, work):
     return torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=work)
 
 
+def matrix_state_recurrence(a, k, v, q, S=None):
+    """a [T, H, N] (or [T, H, 1]), k, q [T, H, N], v [T, H, P]: S_t = diag(a_t) S_(t-1) + k_t v_t^T from S (zeros when
+    None), o_t = S_t^T q_t. Returns (o [T, H, P], the last S [H, N, P])."""
+    T, H, N = k.shape
+    S = torch.zeros(H, N, v.shape[2], dtype=k.dtype) if S is None else S.clone()
+    out = []
+    for t in range(T):
+        S = a[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        out.append(torch.einsum("hnp,hn->hp", S, q[t]))
+    return torch.stack(out), S
+
+
 # ---------------------------------------------------------------- mixer 'parallel' ----
 
 def windowed_conv_attention(h, w, p, m, eps):
@@ -127,12 +139,8 @@ def mamba2(h, w, p, m, eps):
     C = xbc[:, inner + G * N:].reshape(T, G, N).repeat_interleave(Hh // G, dim=1)
     dt = softplus(dt + w[p + "dt_bias"])
     decay = torch.exp(-torch.exp(w[p + "A_log"]) * dt)                 # [T, heads]
-    S = torch.zeros(Hh, N, P, dtype=h.dtype)
-    ys = []
-    for t in range(T):
-        S = decay[t][:, None, None] * S + dt[t][:, None, None] * B[t][:, :, None] * x[t][:, None, :]
-        ys.append(torch.einsum("hnp,hn->hp", S, C[t]) + w[p + "D"][:, None] * x[t])
-    y = torch.stack(ys).reshape(T, inner) * silu(z)
+    y, _ = matrix_state_recurrence(decay[:, :, None], B, dt[:, :, None] * x, C)
+    y = (y + w[p + "D"][:, None] * x).reshape(T, inner) * silu(z)
     parts = m.get("norm_groups", 1)
     y = rms(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * w[p + "norm"]
     return y @ w[p + "o"].T
@@ -168,12 +176,8 @@ def gated_linear_attention(h, w, p, m, eps):
     v = (h @ w[p + "v"].T).reshape(T, Hh, dv)
     z = (h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "a2.b"]
     alpha = (torch.sigmoid(z) ** (1.0 / m["tau"])).reshape(T, Hh, d)
-    S = torch.zeros(Hh, d, dv, dtype=h.dtype)
-    os_ = []
-    for t in range(T):
-        S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        os_.append(torch.einsum("hnp,hn->hp", S, q[t]))
-    o = rms(torch.stack(os_), eps) * w[p + "norm"]
+    o, _ = matrix_state_recurrence(alpha, k, v, q)
+    o = rms(o, eps) * w[p + "norm"]
     return (o.reshape(T, Hh * dv) * silu(h @ w[p + "g"].T)) @ w[p + "o"].T
 
 
@@ -294,3 +298,14 @@ def forward(cfg, w, ids, work=torch.float64, margins=None):
         after.append(xs.sum(dim=0))
     x = rms(xs.sum(dim=0), eps) * w["final.norm"]
     return x @ w["head"].T, torch.stack(after)
+
+
+def greedy_generate(cfg, w, prompt, n, work=torch.float64):
+    """The ``n`` tokens that always taking the largest logit gives after ``prompt`` (the whole sequence is run again for
+    every token: slow and plain)."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        tok = int(torch.argmax(forward(cfg, w, torch.tensor(seq), work)[0][-1]))
+        out.append(tok)
+        seq.append(tok)
+    return out

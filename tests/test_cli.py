@@ -175,3 +175,31 @@ def test_the_commands_serve_a_movalorn_folder_too(tmp_path):
     lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
     assert [[int(t) for t in ln.split()] for ln in lines] == [movalorn_plain.greedy_generate(cfg, w, p, 6) for p in prompts]
     assert any("MovalornConfig" in ln for ln in r.stderr.splitlines())
+
+
+@pytest.mark.gpu
+def test_the_commands_serve_a_fekitar_folder_too(tmp_path):
+    """``random-model`` and ``generate`` with a Fekitar ``config.json``, through the same registry: copies of the stream,
+    mixers side by side, a layer that borrows keys and values, experts with a gated shared expert."""
+    import tiny_fekitar
+    from plain import fekitar_plain
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(tiny_fekitar.R))
+    folder = tmp_path / "model"
+    r = subprocess.run([sys.executable, "-m", "sleuth_b200", "random-model", str(cfg_path), str(folder), "--seed", "3",
+                        "--dtype", "fp32"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    tiny_fekitar.sharpen(folder)
+    cfg, w = plain.read_model(folder)
+    assert cfg["architecture"] == "Fekitar" and w["l0.hc1.mix"].shape == (3, 3) and w["l0.mix.right.in"].shape == (2 * 48 + 2 * 12 + 3, 72)
+    assert w["l1.mix.right.a1"].shape == (5, 72) and "l4.mix.k" not in w and "l2.hc2.in" not in w and w["l0.mlp.shared.sg"].shape == (1, 72)
+    prompts = [[5, 17, 3, 200, 9], [150, 2], [77]]
+    text = "; ".join(",".join(map(str, p)) for p in prompts)
+    r = subprocess.run([sys.executable, "-m", "sleuth_b200", "generate", str(folder), "--prompt-ids", text, "--temperature", "0",
+                        "--max-new-tokens", "6", "--dtype", "fp32", "--max-seq-len", "128"],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    assert [[int(t) for t in ln.split()] for ln in lines] == [fekitar_plain.greedy_generate(cfg, w, p, 6) for p in prompts]
+    assert any("FekitarConfig" in ln for ln in r.stderr.splitlines())

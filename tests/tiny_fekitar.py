@@ -68,12 +68,13 @@ R = {"architecture": "Fekitar", "vocab": 211, "width": 72, "norm": {"eps": 1e-5}
 
 # no copies at all (a plain residual with a multiplier); widths that send bfloat16 prompts through the tensor-memory
 # products and single tokens through the weight-streaming kernel; the differential attention first, lending to two layers;
-# a window of a page and one; whole rotation without scaling; one key/value head a query head
+# a window of a page and one; whole rotation without scaling; one key/value head a query head; both one-map attentions
+# have keys and values of 64 channels, which in bfloat16 sends them through the tensor-core attention kernels
 S = {"architecture": "Fekitar", "vocab": 320, "width": 256, "norm": {"eps": 1e-6}, "residual_mult": 1.0,
      "layers": [diff(att(4, 2, 32, 64, rot={"base": 10000.0, "dims": 32}, diff=0.5), moe(8, 2, 64, shared=128)),
                 par2(att(4, 4, 64, 64, rot={"base": 10000.0, "dims": 64}, softcap=30.0), gla(2, 72, 32, 16.0, 8), 0.7, 1.4, moe(8, 3, 64, limit=3.0)),
                 diff(att(4, 2, 32, 64, conv=3, rot={"base": 10000.0, "dims": 32}, diff=0.5, kv_from=0), None),
-                par(att(4, 2, 32, 32, conv=4, window=65), mamba(4, 32, 72, groups=2, conv=4, norm_groups=2), moe(8, 2, 64, shared=64)),
+                par(att(4, 2, 64, 64, conv=4, window=65), mamba(4, 32, 72, groups=2, conv=4, norm_groups=2), moe(8, 2, 64, shared=64)),
                 diff(att(4, 2, 32, 64, rot={"base": 10000.0, "dims": 32}, diff=0.5, kv_from=0), moe(1, 1, 40, shared=32))]}
 
 # one copy of the stream with coefficients; a window of one token (a token sees itself alone) and one longer than any
