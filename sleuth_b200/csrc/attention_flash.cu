@@ -60,6 +60,7 @@ struct FlashArgs {
   // other score rules (off by default): score <- cap * tanh(score / cap), then score -= slopes[head] * (query position - key position)
   float softcap_log2;           // cap * log2(e), or 0
   const float* slopes;          // [H] or null
+  int out_f32;                  // `out` is float32 [tokens, H * HD] instead of bfloat16
 };
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -269,7 +270,14 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
     if (R >= rows_total) continue;
     if (a.sinks) l_r[h] += exp2f(a.sinks[kh * G + R % G] * kLog2e - m_r[h]);
     const float inv = 1.0f / l_r[h];
-    __nv_bfloat16* dst = a.out + ((size_t)(tok0 + R / G) * a.heads + kh * G + R % G) * HD;
+    const size_t at = ((size_t)(tok0 + R / G) * a.heads + kh * G + R % G) * HD;
+    if (a.out_f32) {
+      float* dst = reinterpret_cast<float*>(a.out) + at;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8 + 2 * t4) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      continue;
+    }
+    __nv_bfloat16* dst = a.out + at;
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
       const uint32_t v = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
@@ -590,7 +598,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     const int head = head0 + row;
     if (a.splits == 1) {
       if (a.sinks) l += exp2f(a.sinks[head] * kLog2e - m_use);
-      a.out[((size_t)tok * a.heads + head) * HD + d] = __float2bfloat16_rn(acc / l);
+      if (a.out_f32) reinterpret_cast<float*>(a.out)[((size_t)tok * a.heads + head) * HD + d] = acc / l;
+      else a.out[((size_t)tok * a.heads + head) * HD + d] = __float2bfloat16_rn(acc / l);
     } else {
       const size_t pi = ((size_t)seq * a.heads + head) * a.splits + split;
       a.part_o[pi * HD + d] = acc;
@@ -647,7 +656,8 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
       m = m_new;
     }
     if (a.sinks) l += exp2f(a.sinks[head] * kLog2e - m);
-    a.out[((size_t)tok * a.heads + head) * HD + d] = __float2bfloat16_rn(acc / l);
+    if (a.out_f32) reinterpret_cast<float*>(a.out)[((size_t)tok * a.heads + head) * HD + d] = acc / l;
+    else a.out[((size_t)tok * a.heads + head) * HD + d] = __float2bfloat16_rn(acc / l);
   }
   if (tid == 0) *counter = 0;
 }
@@ -721,7 +731,8 @@ extern "C" long long slb_attention_decode_scratch_floats(int n_seqs, int heads, 
 static int attention_prefill_any(const void* q, const void* k_pool, const void* v_pool, void* out,
                                  const int* seq_start, const int* past, const int* counts, const int* block_table,
                                  int table_stride, int n_seqs, int max_count, int heads, int kv_heads, int head_dim,
-                                 int window, float scale, const float* sinks, const float* slopes, float softcap, void* stream) {
+                                 int window, float scale, const float* sinks, const float* slopes, float softcap, int out_f32,
+                                 void* stream) {
   SLB_REQUIRE(n_seqs >= 0 && max_count >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention (prefill): seqs=%d max_count=%d heads=%d kv_heads=%d", n_seqs, max_count, heads, kv_heads);
   SLB_REQUIRE(head_dim == 64 || head_dim == 128, "attention (prefill): the tensor-core kernel takes head_dim 64 or 128, got %d", head_dim);
@@ -732,7 +743,7 @@ static int attention_prefill_any(const void* q, const void* k_pool, const void* 
   a.out = (__nv_bfloat16*)out; a.seq_start = seq_start; a.past = past; a.counts = counts;
   a.block_table = block_table; a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads;
   a.window = window; a.scale_log2 = scale * 1.4426950408889634f; a.splits = 1; a.sinks = sinks;
-  a.slopes = slopes; a.softcap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+  a.slopes = slopes; a.softcap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f; a.out_f32 = out_f32;
   return head_dim == 64 ? launch_prefill<64>(a, n_seqs, max_count, (cudaStream_t)stream)
                         : launch_prefill<128>(a, n_seqs, max_count, (cudaStream_t)stream);
 }
@@ -742,16 +753,17 @@ extern "C" int slb_attention_prefill(const void* q, const void* k_pool, const vo
                                      int table_stride, int n_seqs, int max_count, int heads, int kv_heads, int head_dim,
                                      int window, float scale, const float* sinks, void* stream) {
   return attention_prefill_any(q, k_pool, v_pool, out, seq_start, past, counts, block_table, table_stride, n_seqs, max_count, heads,
-                               kv_heads, head_dim, window, scale, sinks, nullptr, 0.0f, stream);
+                               kv_heads, head_dim, window, scale, sinks, nullptr, 0.0f, 0, stream);
 }
 
-// The same kernel with a distance penalty per head (`slopes` [heads] or null) and a soft cap (0 = none) on the scores.
+// The same kernel with a distance penalty per head (`slopes` [heads] or null), a soft cap (0 = none) on the scores, and
+// optionally a float32 result.
 extern "C" int slb_attention_prefill_scored(const void* q, const void* k_pool, const void* v_pool, void* out,
                                             const int* seq_start, const int* past, const int* counts, const int* block_table,
                                             int table_stride, int n_seqs, int max_count, int heads, int kv_heads, int head_dim,
-                                            int window, float scale, const float* slopes, float softcap, void* stream) {
+                                            int window, float scale, const float* slopes, float softcap, int out_f32, void* stream) {
   return attention_prefill_any(q, k_pool, v_pool, out, seq_start, past, counts, block_table, table_stride, n_seqs, max_count, heads,
-                               kv_heads, head_dim, window, scale, nullptr, slopes, softcap, stream);
+                               kv_heads, head_dim, window, scale, nullptr, slopes, softcap, out_f32, stream);
 }
 
 static int attention_decode_any(const void* q, const void* k_pool, const void* v_pool, void* out,
@@ -761,7 +773,7 @@ static int attention_decode_any(const void* q, const void* k_pool, const void* v
                                 long long n_counters, const void* qkv, int qkv_kv_heads, const float* bias,
                                 const float* q_gain, const float* k_gain, const float* cos_table,
                                 const float* sin_table, float eps, const void* next, long long next_bytes,
-                                const float* sinks, const float* slopes, float softcap, void* stream) {
+                                const float* sinks, const float* slopes, float softcap, int out_f32, void* stream) {
   // qkv != null: `q` is ignored; the kernel takes the new token's raw projection rows [n, (H + 2 * qkv_kv_heads) * hd],
   // applies bias, QK-norm and the rotation itself, and (qkv_kv_heads == kv_heads) writes the token's key and value
   // into the cache. cos/sin tables, if given, are [positions, hd / 2]: the whole head rotates.
@@ -792,7 +804,7 @@ static int attention_decode_any(const void* q, const void* k_pool, const void* v
   a.part_ml = scratch ? scratch + (size_t)n_seqs * heads * splits * head_dim : nullptr;
   a.qkv = (const __nv_bfloat16*)qkv; a.qkv_kv_heads = qkv_kv_heads; a.bias = bias; a.q_gain = q_gain; a.k_gain = k_gain;
   a.cos_table = cos_table; a.sin_table = sin_table; a.eps = eps; a.sinks = sinks;
-  a.slopes = slopes; a.softcap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
+  a.slopes = slopes; a.softcap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f; a.out_f32 = out_f32;
   a.pages_after_wait = (qkv == nullptr || qkv_kv_heads == 0 || pdl_mode() == 1) ? 1 : 0;
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "attention (decode): the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
@@ -810,7 +822,7 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
                                     const float* sinks, void* stream) {
   return attention_decode_any(q, k_pool, v_pool, out, seq_start, past, block_table, table_stride, n_seqs, heads, kv_heads, head_dim,
                               window, scale, splits, scratch, scratch_floats, counters, n_counters, qkv, qkv_kv_heads, bias, q_gain,
-                              k_gain, cos_table, sin_table, eps, next, next_bytes, sinks, nullptr, 0.0f, stream);
+                              k_gain, cos_table, sin_table, eps, next, next_bytes, sinks, nullptr, 0.0f, 0, stream);
 }
 
 // One token a sequence with post-processed queries, a distance penalty per head (`slopes` or null) and a soft cap (0 = none).
@@ -819,8 +831,8 @@ extern "C" int slb_attention_decode_scored(const void* q, const void* k_pool, co
                                            int n_seqs, int heads, int kv_heads, int head_dim, int window, float scale,
                                            int splits, float* scratch, long long scratch_floats, int* counters,
                                            long long n_counters, const void* next, long long next_bytes, const float* slopes,
-                                           float softcap, void* stream) {
+                                           float softcap, int out_f32, void* stream) {
   return attention_decode_any(q, k_pool, v_pool, out, seq_start, past, block_table, table_stride, n_seqs, heads, kv_heads, head_dim,
                               window, scale, splits, scratch, scratch_floats, counters, n_counters, nullptr, 0, nullptr, nullptr,
-                              nullptr, nullptr, nullptr, 0.0f, next, next_bytes, nullptr, slopes, softcap, stream);
+                              nullptr, nullptr, nullptr, 0.0f, next, next_bytes, nullptr, slopes, softcap, out_f32, stream);
 }

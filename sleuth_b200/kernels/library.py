@@ -171,16 +171,16 @@ _SIGNATURES = {
     "slb_gemm_tc_gated": [P, P, P, I, I, I, I, I, F, F, P, P],
     "slb_moe_experts": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
     "slb_attention_scored": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, F, I, I, P, L, I, I, P],
-    "slb_attention_prefill_scored": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, F, P],
-    "slb_attention_decode_scored": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P, L, P, L, P, F, P],
+    "slb_attention_prefill_scored": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, F, I, P],
+    "slb_attention_decode_scored": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P, L, P, L, P, F, I, P],
     "slb_sigmoid_gate": [P, P, L, I, I, I, P],
     "slb_causal_conv": [P, L, P, P, P, P, P, P, P, L, I, I, I, I, I, P],
     "slb_decay_scan": [P, L, P, L, P, L, P, L, I, P, L, P, P, P, P, I, I, I, I, I, F, I, P, L, P],
     "slb_step_decay": [P, L, P, P, P, P, I, I, P],
     "slb_channel_decay": [P, P, I, I, F, P],
     "slb_gated_group_norm": [P, P, L, P, I, P, L, P, I, P, I, I, I, I, F, I, P],
-    "slb_unit_post": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P],
-    "slb_diff_combine": [P, P, L, P, I, I, I, F, F, F, I, P],
+    "slb_unit_post": [P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
+    "slb_diff_combine": [P, P, L, P, I, I, I, F, F, F, I, I, P],
     "slb_streams_fill": [P, P, L, I, I, P],
     "slb_hyper_read": [P, P, P, P, L, I, I, F, I, P],
     "slb_hyper_write": [P, P, P, P, L, I, I, F, P],

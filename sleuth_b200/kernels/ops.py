@@ -351,22 +351,24 @@ def _sinks_ok(sinks, heads: int) -> None:
 
 def attention_prefill(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
                       kv_heads: int, head_dim: int, window: int, scale: float, stream=None, sinks=None, slopes=None,
-                      softcap: float = 0.0) -> None:
+                      softcap: float = 0.0, out_f32: bool = False) -> None:
     """Tensor-core attention for a step in which sequences bring any number of tokens. ``sinks`` [heads]: a learned
     score per head in the softmax denominator (as in ``attention``). ``slopes`` [heads] float32 / ``softcap``: the score
-    rules of ``attention_scored`` (not together with sinks)."""
+    rules of ``attention_scored`` (not together with sinks). ``out_f32``: ``out`` is float32."""
     _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table, slopes)
     _sinks_ok(sinks, heads)
     _slopes_ok(slopes, heads, sinks)
     T, n = q.shape[0], block_table.shape[0]
     _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
-    _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tensor cores): bfloat16 only")
+    _need(q.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16 and out.dtype == (torch.float32 if out_f32 else torch.bfloat16),
+          "attention (tensor cores): bfloat16 only")
     _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
     _need(seq_start.numel() >= n + 1 and past.numel() >= n and counts.numel() >= n, "attention: per-sequence tables")
-    if slopes is not None or softcap:
+    _need(not out_f32 or sinks is None, "attention: a float32 result does not go with sinks")
+    if slopes is not None or softcap or out_f32:
         lib().call("slb_attention_prefill_scored", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
                    _p(block_table), block_table.shape[1], n, int(max_count), heads, kv_heads, head_dim, int(window),
-                   float(scale), _p(slopes), float(softcap), stream if stream is not None else current_stream())
+                   float(scale), _p(slopes), float(softcap), 1 if out_f32 else 0, stream if stream is not None else current_stream())
         return
     lib().call("slb_attention_prefill", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
                _p(block_table), block_table.shape[1], n, int(max_count), heads, kv_heads, head_dim, int(window),
@@ -420,7 +422,7 @@ def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, m
 def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads: int, kv_heads: int, head_dim: int,
                      window: int, scale: float, splits: int, scratch, stream=None, qkv=None, qkv_kv_heads: int = 0,
                      bias=None, q_gain=None, k_gain=None, cos=None, sin=None, eps: float = 1e-6, next_read=None,
-                     sinks=None, slopes=None, softcap: float = 0.0) -> None:
+                     sinks=None, slopes=None, softcap: float = 0.0, out_f32: bool = False) -> None:
     """Tensor-core attention for a step in which every sequence brings one token (split-KV).
 
     With ``qkv`` (the raw fused projection ``[n, (heads + 2 * qkv_kv_heads) * head_dim]``) the kernel also does what
@@ -434,8 +436,9 @@ def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads
     _slopes_ok(slopes, heads, sinks)
     _need(not (slopes is not None or softcap) or qkv is None, "attention (decode): other score rules go with post-processed queries")
     n = block_table.shape[0]
-    _need(out.shape == (n, heads * head_dim) and out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16,
-          "attention (tensor cores): shapes disagree or not bfloat16")
+    _need(out.shape == (n, heads * head_dim) and k_pool.dtype == v_pool.dtype == torch.bfloat16
+          and out.dtype == (torch.float32 if out_f32 else torch.bfloat16), "attention (tensor cores): shapes disagree or not bfloat16")
+    _need(not out_f32 or (sinks is None and qkv is None), "attention: a float32 result goes with post-processed queries and no sinks")
     _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
     _need(scratch is None or scratch.dtype == torch.float32, "attention: scratch is float32")
     if qkv is None:
@@ -446,12 +449,12 @@ def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads
             _need(v is None or v.dtype == torch.float32, "attention: gains, biases and tables are float32")
         _need(cos is None or (cos.shape[1] == head_dim // 2 and sin.shape == cos.shape), "attention: rotation tables")
     counters = _decode_counters(out.device, n * kv_heads * ((heads // kv_heads + 15) // 16)) if splits > 1 else None
-    if slopes is not None or softcap:
+    if slopes is not None or softcap or out_f32:
         lib().call("slb_attention_decode_scored", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past),
                    _p(block_table), block_table.shape[1], n, heads, kv_heads, head_dim, int(window), float(scale),
                    int(splits), _p(scratch), 0 if scratch is None else scratch.numel(), _p(counters),
                    0 if counters is None else counters.numel(), _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read),
-                   _p(slopes), float(softcap), stream if stream is not None else current_stream())
+                   _p(slopes), float(softcap), 1 if out_f32 else 0, stream if stream is not None else current_stream())
         return
     lib().call("slb_attention_decode", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past),
                _p(block_table), block_table.shape[1], n, heads, kv_heads, head_dim, int(window), float(scale),
@@ -1203,38 +1206,43 @@ def gated_group_norm(y, gate, gain, out, groups: int, eps: float, gate_first: bo
 
 
 def unit_post(rows, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table, heads: int, kv_heads: int,
-              maps: int, dim: int, vdim: int, rot: int, eps: float, stream=None) -> None:
+              maps: int, dim: int, vdim: int, rot: int, eps: float, stream=None, pad: int = 0) -> None:
     """float32 rows [q units | k units | v units] -> q_out [T, heads * maps, dim] and the token's cache rows (keys
     [pages, kv_heads, 64, maps * dim], values [pages, kv_heads, 64, vdim]); without pools the rows hold q units only.
-    q and k units: RMS norm with the gain when one is given, then the first ``rot`` channels turn in pairs (i, i + rot/2)."""
+    q and k units: RMS norm with the gain when one is given, then the first ``rot`` channels turn in pairs (i, i + rot/2).
+    ``pad`` W: q rows, key rows and value rows are all W wide; map m's channels sit at m * dim of a q row whose other
+    channels are set to zero, and the cache's spare channels are left alone (they are zero from the start), so that a
+    kernel that takes q . k over W channels forms the map's own score."""
     _cuda(q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table)
     T = q_out.shape[0]
     writes = k_pool is not None
     width = heads * maps * dim + (kv_heads * maps * dim + kv_heads * vdim if writes else 0)
     rs = _rows_f32(rows, width, "unit_post")
-    _need(q_out.shape == (T, heads * maps, dim) and q_out.dtype in DT and rows.shape[0] == T, "unit_post: the query buffer")
+    qw, kw, vw = (pad, pad, pad) if pad else (dim, maps * dim, vdim)
+    _need(q_out.shape == (T, heads * maps, qw) and q_out.dtype in DT and rows.shape[0] == T, "unit_post: the query buffer")
     for g in (q_gain, k_gain):
         _need(g is None or (g.dtype == torch.float32 and g.numel() == dim), "unit_post: gains are float32 [dim]")
     if rot:
         _need(cos is not None and cos.dtype == torch.float32 and cos.shape[1] == rot // 2 and sin.shape == cos.shape, "unit_post: rotation tables")
     stride = 0
     if writes:
-        _need(k_pool.dtype == v_pool.dtype == q_out.dtype and tuple(k_pool.shape[1:]) == (kv_heads, 64, maps * dim)
-              and tuple(v_pool.shape[1:]) == (kv_heads, 64, vdim), "unit_post: cache pools")
+        _need(k_pool.dtype == v_pool.dtype == q_out.dtype and tuple(k_pool.shape[1:]) == (kv_heads, 64, kw)
+              and tuple(v_pool.shape[1:]) == (kv_heads, 64, vw), "unit_post: cache pools")
         _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "unit_post: block table")
         stride = block_table.shape[1]
     lib().call("slb_unit_post", _p(rows), rs, _p(q_gain), _p(k_gain), _p(cos), _p(sin), _p(q_out), _p(k_pool), _p(v_pool),
                _p(tok_seq), _p(tok_pos), _p(block_table) if writes else None, stride, T, heads, kv_heads, maps, dim, vdim, int(rot),
-               1 if writes else 0, float(eps), DT[q_out.dtype], _st(stream))
+               1 if writes else 0, float(eps), int(pad), DT[q_out.dtype], _st(stream))
 
 
-def diff_combine(a, gate, out, heads: int, vdim: int, lam: float, post: float, eps: float, stream=None) -> None:
-    """out[t, h] = (a[t, h, 0] - lam * a[t, h, 1]) / rms * post * sigmoid(gate[t, h]); a float32 [T, heads * 2, vdim]."""
+def diff_combine(a, gate, out, heads: int, vdim: int, lam: float, post: float, eps: float, stream=None, row: int = 0) -> None:
+    """out[t, h] = (a[t, h, 0] - lam * a[t, h, 1]) / rms * post * sigmoid(gate[t, h]); a float32 [T, heads * 2, row] of which
+    the first vdim values of a row count (``row`` 0 = vdim)."""
     _cuda(a, out)
     T = out.shape[0]
-    _need(a.dtype == torch.float32 and a.numel() == T * heads * 2 * vdim and out.shape == (T, heads * vdim) and out.dtype in DT, "diff_combine: shapes")
+    _need(a.dtype == torch.float32 and a.numel() == T * heads * 2 * (row or vdim) and out.shape == (T, heads * vdim) and out.dtype in DT, "diff_combine: shapes")
     gs = _rows_f32(gate, heads, "diff_combine gate") if gate is not None else 0
-    lib().call("slb_diff_combine", _p(a), _p(gate), gs, _p(out), T, heads, vdim, float(lam), float(post), float(eps), DT[out.dtype], _st(stream))
+    lib().call("slb_diff_combine", _p(a), _p(gate), gs, _p(out), T, heads, vdim, float(lam), float(post), float(eps), int(row), DT[out.dtype], _st(stream))
 
 
 def streams_fill(x0, xs, streams: int, stream=None) -> None:

@@ -52,11 +52,18 @@ class ScoredAttention(Part):
         if s.slope_exponent > 0:
             self.slopes = torch.tensor([2.0 ** (-s.slope_exponent * (h + 1) / s.heads) for h in range(s.heads)],
                                        dtype=torch.float32, device=ctx.device)
+        self.slopes_maps = self.slopes.repeat_interleave(s.maps).contiguous() if self.slopes is not None else None   # one a (head, map)
         self.qkvg = self.o = self.conv = self.q_gain = self.k_gain = None
         self.lam = 0.0
         # one map, bfloat16, keys and values of one width that the tensor-core kernels take: prompts and single tokens run
         # on the mma.sync kernels (which know the soft cap and the distance penalty); everything else on the general kernel
         self.flash = s.maps == 1 and s.value_dim == s.head_dim and ops.flash_supported(s.head_dim, ctx.dtype)
+        # two maps in bfloat16 whose key row (both maps) and value row fit 128 channels: rows of 64 or 128 channels with zero
+        # channels at the end. A query of map m is zero outside the map's own channels, so the same tensor-core kernels form
+        # q_m . k_m as a product over the whole row, with 2 * heads query heads; their results come out in float32.
+        self.pad = 0
+        if s.maps == 2 and ctx.dtype == torch.bfloat16 and max(2 * s.head_dim, s.value_dim) <= 128 and (2 * s.heads) % s.kv_heads == 0:
+            self.pad = 64 if max(2 * s.head_dim, s.value_dim) <= 64 else 128
 
     def _proj(self):
         return ["q"] if self.spec.reads_shared_kv else ["q", "k", "v"]
@@ -100,7 +107,8 @@ class ScoredAttention(Part):
         s = self.spec
         parts = []
         if not s.reads_shared_kv:
-            parts.append(("kv", KVRequest(s.kv_heads, s.maps * s.head_dim, s.window, s.value_dim)))
+            parts.append(("kv", KVRequest(s.kv_heads, self.pad, s.window) if self.pad else
+                          KVRequest(s.kv_heads, s.maps * s.head_dim, s.window, s.value_dim)))
         if s.conv_taps > 1:
             parts.append(("tail", StateRequest((s.conv_taps - 1, self.nq + self.nk + self.nv), torch.float32)))
         return BundleRequest(tuple(parts)) if parts else None
@@ -125,10 +133,10 @@ class ScoredAttention(Part):
             ops.causal_conv(p, self.conv, None, view["tail"].state, b.slots, b.tok_seq, b.seq_start, rows, False, b.stream)
         tables = self.position.tables()
         cos, sin = tables if tables is not None else (None, None)
-        q = ws.take((T, s.heads * s.maps, s.head_dim), dt)
+        q = ws.take((T, s.heads * s.maps, self.pad or s.head_dim), dt)
         ops.unit_post(rows, self.q_gain, self.k_gain, cos, sin, q, kv.k_pool if writes else None, kv.v_pool if writes else None,
                       b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads, s.maps, s.head_dim, s.value_dim,
-                      self.position.rot_dim, s.eps, b.stream)
+                      self.position.rot_dim, s.eps, b.stream, pad=self.pad)
         gate = p[:, nqkv:] if self.ng else None
         y = ws.take((T, s.heads * s.value_dim), dt)
         if self.flash:
@@ -148,6 +156,21 @@ class ScoredAttention(Part):
             ops.attention_scored(q, kv.k_pool, kv.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads, s.head_dim,
                                  kv.window, self.scale, b.stream, slopes=self.slopes, softcap=s.softcap, gate=gate,
                                  value_dim=s.value_dim)
+        elif self.pad:
+            W = self.pad
+            a = ws.take((T, s.heads * 2 * W), torch.float32)
+            if b.max_count == 1:
+                splits = ops.decode_splits(b.n, s.kv_heads, 2 * s.heads // s.kv_heads, table.shape[1])
+                floats = ops.decode_scratch_floats(b.n, 2 * s.heads, W, splits)
+                scratch = ws.take((floats,), torch.float32) if floats else None
+                ops.attention_decode(q, kv.k_pool, kv.v_pool, a, b.seq_start, b.past, table, 2 * s.heads, s.kv_heads, W, kv.window,
+                                     self.scale, splits, scratch, b.stream, next_read=self.o.weight, slopes=self.slopes_maps,
+                                     softcap=s.softcap, out_f32=True)
+            else:
+                ops.attention_prefill(q, kv.k_pool, kv.v_pool, a, b.seq_start, b.past, b.counts, table, b.max_count, 2 * s.heads,
+                                      s.kv_heads, W, kv.window, self.scale, b.stream, slopes=self.slopes_maps, softcap=s.softcap,
+                                      out_f32=True)
+            ops.diff_combine(a, gate, y, s.heads, s.value_dim, self.lam, 1.0 - s.diff, s.eps, b.stream, row=W)
         else:
             a = ws.take((T, s.heads * 2, s.value_dim), torch.float32)
             ops.attention_scored(q, kv.k_pool, kv.v_pool, a, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads, s.head_dim,

@@ -179,7 +179,7 @@ def test_gated_group_norm_in_both_orders(inner, groups, gate_first, dtype):
 
 # ---------------------------------------------------------------- attention ----
 
-def attention_case(o, dtype, H, G, d, dv, maps, lengths, pasts, window, slopes, softcap, rot, norm, loud, flash=False):
+def attention_case(o, dtype, H, G, d, dv, maps, lengths, pasts, window, slopes, softcap, rot, norm, loud, flash=False, pad=0):
     """Write whole sequences into a paged cache through ``unit_post`` (in two steps: ``pasts`` tokens, then the rest) and
     attend from the second step's tokens. ``loud``: (distance) -> one key at that distance behind the LAST query of each
     sequence gets a large score."""
@@ -195,6 +195,10 @@ def attention_case(o, dtype, H, G, d, dv, maps, lengths, pasts, window, slopes, 
         at += k
     k_pool = torch.full((total, G, 64, maps * d), 7.0, dtype=dtype, device=DEV)      # stale contents must never be read
     v_pool = torch.full((total, G, 64, dv), 7.0, dtype=dtype, device=DEV)
+    if pad:         # rows widened to ``pad`` channels: the spare channels are zero from the start and nobody writes them
+        k_pool, v_pool = (torch.zeros((total, G, 64, pad), dtype=dtype, device=DEV) for _ in range(2))
+        k_pool[..., :maps * d] = 7.0
+        v_pool[..., :dv] = 7.0
     width = H * maps * d + G * maps * d + G * dv
     rows = [torch.randn(L, width + 2, generator=g) for L in lengths]
     qg, kg = (torch.randn(d, generator=g) + 1 for _ in range(2))
@@ -221,10 +225,26 @@ def attention_case(o, dtype, H, G, d, dv, maps, lengths, pasts, window, slopes, 
         tok_seq, tok_pos, _ = batch_tables([counts[i] for i in live], [begin[i] for i in live])
         tab = table[live].contiguous().to(DEV)
         T = part.shape[0]
-        q = torch.empty(T, H * maps, d, dtype=dtype, device=DEV)
+        q = torch.full((T, H * maps, pad or d), 5.0, dtype=dtype, device=DEV)
         o.unit_post(part[:, :width], qg.to(DEV) if norm else None, kg.to(DEV) if norm else None, None if cos is None else cos.to(DEV),
-                    None if sin is None else sin.to(DEV), q, k_pool, v_pool, tok_seq, tok_pos, tab, H, G, maps, d, dv, rot, 1e-6)
+                    None if sin is None else sin.to(DEV), q, k_pool, v_pool, tok_seq, tok_pos, tab, H, G, maps, d, dv, rot, 1e-6, pad=pad)
         if step == 0:
+            continue
+        if pad:         # 2 H query heads over rows of ``pad`` channels on the tensor-core kernels, float32 results
+            counts_live = [counts[i] for i in live]
+            _, _, start = batch_tables(counts_live)
+            past_d, counts_d = i32([begin[i] for i in live]), i32(counts_live)
+            wide = torch.empty(T, H * maps * pad, device=DEV)
+            if max(counts_live) == 1:
+                scratch = torch.empty(o.decode_scratch_floats(len(live), H * maps, pad, 2), device=DEV)
+                o.attention_decode(q, k_pool, v_pool, wide, start, past_d, tab, H * maps, G, pad, window, 0.3, 2, scratch, out_f32=True)
+            else:
+                o.attention_prefill(q, k_pool, v_pool, wide, start, past_d, counts_d, tab, max(counts_live), H * maps, G, pad, window, 0.3,
+                                    out_f32=True)
+            at = 0
+            for i in live:
+                got.append(wide.view(T, H * maps, pad)[at:at + counts[i], :, :dv].float().cpu())
+                at += counts[i]
             continue
         out = torch.empty(T, H * maps, dv, dtype=torch.float32 if maps > 1 else dtype, device=DEV)
         if flash:       # the tensor-core kernels: single tokens through the split-KV kernel, the rest through the prompt kernel
@@ -313,6 +333,19 @@ def test_the_tensor_core_kernels_know_the_penalty_and_the_cap(d, window, softcap
             got, want = attention_case(o, torch.bfloat16, H, G, d, d, 1, lengths, pasts, window, slopes, softcap, d, True, loud, flash=True)
             for a, b in zip(got, want):
                 torch.testing.assert_close(a.double(), b, **tol)
+
+
+@pytest.mark.parametrize("H,G,d,dv,rot,pad", [(2, 1, 16, 40, 8, 64), (4, 2, 32, 64, 32, 64), (4, 1, 48, 96, 48, 128), (3, 3, 8, 16, 0, 64),
+                                              (8, 4, 64, 128, 64, 128)])
+def test_two_maps_on_the_tensor_core_kernels(H, G, d, dv, rot, pad):
+    """Differential attention's two maps as 2 H query heads over widened rows: a query is zero outside its map's channels,
+    the cache's spare channels are zero, so the kernels' products over the whole row are the maps' own scores."""
+    o = ops()
+    tol = dict(rtol=3e-2, atol=3e-2)
+    for lengths, pasts, loud in (([400, 66, 1], [0, 0, 0], 333), ([400, 129], [399, 128], 333), ([200, 65], [63, 2], 63)):
+        got, want = attention_case(o, torch.bfloat16, H, G, d, dv, 2, lengths, pasts, 0, None, 0.0, rot, False, loud, pad=pad)
+        for a, b in zip(got, want):
+            torch.testing.assert_close(a.double(), b, **tol)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
