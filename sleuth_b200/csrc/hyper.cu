@@ -56,6 +56,94 @@ __global__ void __launch_bounds__(256) hyper_read_kernel(const float* __restrict
   }
 }
 
+// The same with 16-byte loads for widths that are multiples of 4 up to 1,024 * CH: a thread keeps its CH pieces of the
+// weighted sum in registers between the sum of squares and the store, so the copies are read once.
+template <typename T, int CH>
+__global__ void __launch_bounds__(256) hyper_read_vec_kernel(const float* __restrict__ xs, const float* __restrict__ coef,
+                                                             const float* __restrict__ gain, T* __restrict__ out, int d, int S,
+                                                             float eps) {
+  pdl_enter();
+  __shared__ float scratch[33];
+  const float4* row = reinterpret_cast<const float4*>(xs + (size_t)blockIdx.x * S * d);
+  const int d4 = d >> 2;
+  float w[kMaxStreams];
+#pragma unroll
+  for (int s = 0; s < kMaxStreams; ++s) w[s] = s < S ? (coef ? coef[s] : 1.0f) : 0.0f;
+  float4 u[CH];
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + j * 256;
+    u[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < d4) {
+#pragma unroll
+      for (int s = 0; s < kMaxStreams; ++s) {
+        if (s < S) {
+          const float4 v = row[(size_t)s * d4 + c];
+          u[j].x = fmaf(w[s], v.x, u[j].x);
+          u[j].y = fmaf(w[s], v.y, u[j].y);
+          u[j].z = fmaf(w[s], v.z, u[j].z);
+          u[j].w = fmaf(w[s], v.w, u[j].w);
+        }
+      }
+      ss += (u[j].x * u[j].x + u[j].y * u[j].y) + (u[j].z * u[j].z + u[j].w * u[j].w);
+    }
+  }
+  const float r = 1.0f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+  T* o = out + (size_t)blockIdx.x * d;
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int c = threadIdx.x + j * 256;
+    if (c < d4) {
+      const float4 g = reinterpret_cast<const float4*>(gain)[c];
+      o[4 * c + 0] = from_f32<T>(u[j].x * r * g.x);
+      o[4 * c + 1] = from_f32<T>(u[j].y * r * g.y);
+      o[4 * c + 2] = from_f32<T>(u[j].z * r * g.z);
+      o[4 * c + 3] = from_f32<T>(u[j].w * r * g.w);
+    }
+  }
+}
+
+// One thread per (token, four channels): the same arithmetic as hyper_write_kernel with 16-byte loads and stores.
+__global__ void __launch_bounds__(256) hyper_write_vec_kernel(float* __restrict__ xs, const float* __restrict__ y,
+                                                              const float* __restrict__ mix, const float* __restrict__ out_coef,
+                                                              long long rows, int d, int S, float mult) {
+  pdl_enter();
+  const int d4 = d >> 2;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * d4) return;
+  const long long t = i / d4;
+  const int c = (int)(i - t * d4);
+  float4* base = reinterpret_cast<float4*>(xs + (size_t)t * S * d) + c;
+  float4 old[kMaxStreams];
+#pragma unroll
+  for (int s = 0; s < kMaxStreams; ++s) old[s] = s < S ? base[(size_t)s * d4] : make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 yv = reinterpret_cast<const float4*>(y)[i];
+  yv.x *= mult; yv.y *= mult; yv.z *= mult; yv.w *= mult;
+#pragma unroll
+  for (int r = 0; r < kMaxStreams; ++r) {
+    if (r < S) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (mix) {
+#pragma unroll
+        for (int s = 0; s < kMaxStreams; ++s) {
+          if (s < S) {
+            const float m = mix[s * S + r];
+            v.x = fmaf(m, old[s].x, v.x);
+            v.y = fmaf(m, old[s].y, v.y);
+            v.z = fmaf(m, old[s].z, v.z);
+            v.w = fmaf(m, old[s].w, v.w);
+          }
+        }
+      } else {
+        v = old[r];
+      }
+      const float oc = out_coef ? out_coef[r] : 1.0f;
+      base[(size_t)r * d4] = make_float4(fmaf(oc, yv.x, v.x), fmaf(oc, yv.y, v.y), fmaf(oc, yv.z, v.z), fmaf(oc, yv.w, v.w));
+    }
+  }
+}
+
 // One thread per (token, channel). mix: [S, S] indexed [from, to], or null (the identity); out_coef: [S] or null (ones).
 __global__ void __launch_bounds__(256) hyper_write_kernel(float* __restrict__ xs, const float* __restrict__ y,
                                                           const float* __restrict__ mix, const float* __restrict__ out_coef,
@@ -169,6 +257,22 @@ extern "C" int slb_hyper_read(const float* xs, const float* coef, const float* g
               rows, d, S, kMaxStreams);
   if (rows == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  if (d % 4 == 0 && d <= 4096 && (uintptr_t)xs % 16 == 0 && (uintptr_t)gain % 16 == 0) {
+    const dim3 grid((unsigned)rows), block(256);
+    const int ch = d <= 1024 ? 1 : (d <= 2048 ? 2 : 4);
+    if (dtype == kF32) {
+      if (ch == 1) launch(hyper_read_vec_kernel<float, 1>, grid, block, 0, s, xs, coef, gain, (float*)out, d, S, eps);
+      else if (ch == 2) launch(hyper_read_vec_kernel<float, 2>, grid, block, 0, s, xs, coef, gain, (float*)out, d, S, eps);
+      else launch(hyper_read_vec_kernel<float, 4>, grid, block, 0, s, xs, coef, gain, (float*)out, d, S, eps);
+    } else if (dtype == kBF16) {
+      if (ch == 1) launch(hyper_read_vec_kernel<__nv_bfloat16, 1>, grid, block, 0, s, xs, coef, gain, (__nv_bfloat16*)out, d, S, eps);
+      else if (ch == 2) launch(hyper_read_vec_kernel<__nv_bfloat16, 2>, grid, block, 0, s, xs, coef, gain, (__nv_bfloat16*)out, d, S, eps);
+      else launch(hyper_read_vec_kernel<__nv_bfloat16, 4>, grid, block, 0, s, xs, coef, gain, (__nv_bfloat16*)out, d, S, eps);
+    } else {
+      return fail(1, "hyper_read: unknown dtype %d", dtype);
+    }
+    return check_launch("hyper_read");
+  }
   if (dtype == kF32) launch(hyper_read_kernel<float>, dim3((unsigned)rows), dim3(256), 0, s, xs, coef, gain, (float*)out, d, S, eps);
   else if (dtype == kBF16) launch(hyper_read_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(256), 0, s, xs, coef, gain, (__nv_bfloat16*)out, d, S, eps);
   else return fail(1, "hyper_read: unknown dtype %d", dtype);
@@ -180,7 +284,10 @@ extern "C" int slb_hyper_write(float* xs, const float* y, const float* mix, cons
   SLB_REQUIRE(rows >= 0 && d > 0 && S >= 1 && S <= kMaxStreams, "hyper_write: rows=%lld d=%d streams=%d (at most %d)", rows, d, S,
               kMaxStreams);
   if (rows == 0) return 0;
-  launch(hyper_write_kernel, per_element(rows * d), dim3(256), 0, (cudaStream_t)stream, xs, y, mix, out_coef, rows, d, S, mult);
+  if (d % 4 == 0 && (uintptr_t)xs % 16 == 0 && (uintptr_t)y % 16 == 0)
+    launch(hyper_write_vec_kernel, per_element(rows * (d / 4)), dim3(256), 0, (cudaStream_t)stream, xs, y, mix, out_coef, rows, d, S, mult);
+  else
+    launch(hyper_write_kernel, per_element(rows * d), dim3(256), 0, (cudaStream_t)stream, xs, y, mix, out_coef, rows, d, S, mult);
   return check_launch("hyper_write");
 }
 

@@ -68,6 +68,44 @@ __global__ void __launch_bounds__(256) conv_state_kernel(const float* __restrict
     if (k < taps - 1) st[(size_t)k * C] = keep[k];
 }
 
+// Steps that bring few tokens a sequence (single tokens above all): one thread per (sequence, channel) walks the
+// sequence's tokens with the window of the last taps inputs in registers, writes the outputs and leaves the new tail, in
+// one launch. The sums run in the same order as in causal_conv_kernel.
+__global__ void __launch_bounds__(128) causal_conv_short_kernel(const float* __restrict__ in, long long in_stride,
+                                                                const float* __restrict__ w, const float* __restrict__ bias,
+                                                                float* __restrict__ state, const int* __restrict__ slots,
+                                                                const int* __restrict__ seq_start, float* __restrict__ out,
+                                                                long long out_stride, int n_seqs, int C, int taps, int act) {
+  pdl_enter();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n_seqs * C) return;
+  const int seq = (int)(i / C), c = (int)(i - (long long)seq * C);
+  float* st = state + ((size_t)slots[seq] * (taps - 1)) * C + c;
+  float win[kMaxTaps], wt[kMaxTaps];
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) {
+    win[k] = k < taps - 1 ? st[(size_t)k * C] : 0.0f;          // win[0 .. taps-2]: the tail, oldest first
+    wt[k] = k < taps ? w[(size_t)c * taps + k] : 0.0f;
+  }
+  const float b = bias ? bias[c] : 0.0f;
+  for (int t = seq_start[seq]; t < seq_start[seq + 1]; ++t) {
+    const float u = in[(size_t)t * in_stride + c];
+    float acc = b;
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k)
+      if (k < taps - 1) acc = fmaf(wt[k], win[k], acc);
+    acc = fmaf(wt[taps - 1], u, acc);
+    out[(size_t)t * out_stride + c] = act ? silu_f(acc) : acc;
+#pragma unroll
+    for (int k = 0; k < kMaxTaps - 1; ++k)
+      if (k < taps - 2) win[k] = win[k + 1];
+    if (taps > 1) win[taps - 2] = u;
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k)
+    if (k < taps - 1) st[(size_t)k * C] = win[k];
+}
+
 struct ScanArgs {
   const float *q, *k, *v, *a, *vs;     // rows of tokens; vs may be null
   long long q_stride, k_stride, v_stride, a_stride, vs_stride;
@@ -89,8 +127,10 @@ struct ScanArgs {
 // One thread per (sequence, head, value channel p) keeps column p of the head's state, N values, in registers and walks
 // the sequence's tokens of the step. Neighbouring threads hold neighbouring p, so state and value accesses are whole
 // lines and the key, query and decay values of a token are the same addresses for a whole warp. A token's loads do not
-// depend on the state, so the compiler keeps several tokens' loads in flight.
-template <int NB>
+// depend on the state, so the compiler keeps several tokens' loads in flight. LOCAL: the pass that walks a chunk from a
+// zero state for its end state alone (no queries, no outputs). VEC: rows of keys, queries and decays are read four
+// values at a time (N a multiple of 4, rows 16-byte aligned).
+template <int NB, bool LOCAL, bool VEC>
 __global__ void __launch_bounds__(128) decay_scan_kernel(ScanArgs a) {
   pdl_enter();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -113,7 +153,7 @@ __global__ void __launch_bounds__(128) decay_scan_kernel(ScanArgs a) {
   }
   float S[NB];
 #pragma unroll
-  for (int n = 0; n < NB; ++n) S[n] = (n < N && a.mode != 1) ? st[(size_t)n * a.P] : 0.0f;
+  for (int n = 0; n < NB; ++n) S[n] = (n < N && !LOCAL) ? st[(size_t)n * a.P] : 0.0f;
   for (int t = t0; t < t1; ++t) {
     const float* qr = a.q + (size_t)t * a.q_stride + (size_t)g * N;
     const float* kr = a.k + (size_t)t * a.k_stride + (size_t)g * N;
@@ -122,15 +162,37 @@ __global__ void __launch_bounds__(128) decay_scan_kernel(ScanArgs a) {
     if (a.vs) v *= a.vs[(size_t)t * a.vs_stride + h];
     const float a_head = a.a_per_channel ? 1.0f : ar[0];
     float o = 0.0f;
+    if constexpr (VEC) {
 #pragma unroll
-    for (int n = 0; n < NB; ++n) {
-      if (n < N) {
-        const float an = a.a_per_channel ? ar[n] : a_head;
-        S[n] = fmaf(an, S[n], kr[n] * v);
-        o = fmaf(S[n], qr[n], o);
+      for (int n = 0; n < NB; n += 4) {
+        if (n < N) {
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + n);
+          float4 a4 = make_float4(a_head, a_head, a_head, a_head);
+          if (a.a_per_channel) a4 = *reinterpret_cast<const float4*>(ar + n);
+          S[n] = fmaf(a4.x, S[n], k4.x * v);
+          S[n + 1] = fmaf(a4.y, S[n + 1], k4.y * v);
+          S[n + 2] = fmaf(a4.z, S[n + 2], k4.z * v);
+          S[n + 3] = fmaf(a4.w, S[n + 3], k4.w * v);
+          if constexpr (!LOCAL) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qr + n);
+            o = fmaf(S[n], q4.x, o);
+            o = fmaf(S[n + 1], q4.y, o);
+            o = fmaf(S[n + 2], q4.z, o);
+            o = fmaf(S[n + 3], q4.w, o);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < NB; ++n) {
+        if (n < N) {
+          const float an = a.a_per_channel ? ar[n] : a_head;
+          S[n] = fmaf(an, S[n], kr[n] * v);
+          if constexpr (!LOCAL) o = fmaf(S[n], qr[n], o);
+        }
       }
     }
-    if (a.mode != 1) a.out[(size_t)t * ((size_t)a.heads * a.P) + (size_t)h * a.P + p] = o * a.q_scale;
+    if constexpr (!LOCAL) a.out[(size_t)t * ((size_t)a.heads * a.P) + (size_t)h * a.P + p] = o * a.q_scale;
   }
   if (a.mode == 2) return;
 #pragma unroll
@@ -251,12 +313,18 @@ using namespace slb;
 
 extern "C" int slb_causal_conv(const float* in, long long in_stride, const float* w, const float* bias, float* state,
                                const int* slots, const int* tok_seq, const int* seq_start, float* out,
-                               long long out_stride, int tokens, int n_seqs, int C, int taps, int act, void* stream) {
+                               long long out_stride, int tokens, int n_seqs, int C, int taps, int act, int max_count, void* stream) {
   SLB_REQUIRE(tokens >= 0 && n_seqs >= 0 && C > 0 && taps >= 1 && taps <= kMaxTaps, "causal_conv: tokens=%d channels=%d taps=%d",
               tokens, C, taps);
   SLB_REQUIRE(in_stride >= C && out_stride >= C, "causal_conv: rows are narrower than the channels");
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  if (max_count >= 1 && max_count <= 4 && taps > 1) {       // few tokens a sequence: outputs and the new tail in one launch
+    const long long st = (long long)n_seqs * C;
+    launch(causal_conv_short_kernel, dim3((unsigned)((st + 127) / 128)), dim3(128), 0, s, in, in_stride, w, bias, state, slots, seq_start,
+           out, out_stride, n_seqs, C, taps, act);
+    return check_launch("causal_conv (short steps)");
+  }
   const long long total = (long long)tokens * C;
   launch(causal_conv_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, in, in_stride, w, bias,
          (const float*)state, slots, tok_seq, seq_start, out, out_stride, tokens, C, taps, act);
@@ -268,14 +336,29 @@ extern "C" int slb_causal_conv(const float* in, long long in_stride, const float
   return check_launch("conv_state");
 }
 
+template <int NB>
+static void launch_scan_nb(const ScanArgs& g, dim3 grid, dim3 block, bool vec, cudaStream_t s) {
+  if (g.mode == 1) {
+    if (vec) launch(decay_scan_kernel<NB, true, true>, grid, block, 0, s, g);
+    else launch(decay_scan_kernel<NB, true, false>, grid, block, 0, s, g);
+  } else {
+    if (vec) launch(decay_scan_kernel<NB, false, true>, grid, block, 0, s, g);
+    else launch(decay_scan_kernel<NB, false, false>, grid, block, 0, s, g);
+  }
+}
+
 static void launch_scan(const ScanArgs& g, cudaStream_t s) {
   const long long total = (long long)g.n_seqs * (g.mode == 0 ? 1 : g.chunks) * g.heads * g.P;
   const dim3 grid((unsigned)((total + 127) / 128)), block(128);
-  if (g.N <= 16) launch(decay_scan_kernel<16>, grid, block, 0, s, g);
-  else if (g.N <= 32) launch(decay_scan_kernel<32>, grid, block, 0, s, g);
-  else if (g.N <= 64) launch(decay_scan_kernel<64>, grid, block, 0, s, g);
-  else if (g.N <= 128) launch(decay_scan_kernel<128>, grid, block, 0, s, g);
-  else launch(decay_scan_kernel<256>, grid, block, 0, s, g);
+  // four values a load where every row of keys, queries and decays starts on a 16-byte boundary (the sum's order is the same)
+  const bool vec = g.N % 4 == 0 && g.q_stride % 4 == 0 && g.k_stride % 4 == 0 && ((uintptr_t)g.q % 16 == 0) && ((uintptr_t)g.k % 16 == 0) &&
+                   (!g.a_per_channel || (g.a_stride % 4 == 0 && (uintptr_t)g.a % 16 == 0));
+  if (g.N <= 16) launch_scan_nb<16>(g, grid, block, vec, s);
+  else if (g.N <= 32) launch_scan_nb<32>(g, grid, block, vec, s);
+  else if (g.N <= 64) launch_scan_nb<64>(g, grid, block, vec, s);
+  else if (g.N <= 128) launch_scan_nb<128>(g, grid, block, vec, s);
+  else if (g.mode == 1) launch(decay_scan_kernel<256, true, false>, grid, block, 0, s, g);      // (registers spill here either way)
+  else launch(decay_scan_kernel<256, false, false>, grid, block, 0, s, g);
 }
 
 // Portions of more than kScanWhole tokens run in chunks (three passes); the chunk length grows with the portion so that

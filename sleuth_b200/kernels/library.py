@@ -174,7 +174,7 @@ _SIGNATURES = {
     "slb_attention_prefill_scored": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, F, I, P],
     "slb_attention_decode_scored": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P, L, P, L, P, F, I, P],
     "slb_sigmoid_gate": [P, P, L, I, I, I, P],
-    "slb_causal_conv": [P, L, P, P, P, P, P, P, P, L, I, I, I, I, I, P],
+    "slb_causal_conv": [P, L, P, P, P, P, P, P, P, L, I, I, I, I, I, I, P],
     "slb_decay_scan": [P, L, P, L, P, L, P, L, I, P, L, P, P, P, P, I, I, I, I, I, F, I, P, L, P],
     "slb_step_decay": [P, L, P, P, P, P, I, I, P],
     "slb_channel_decay": [P, P, I, I, F, P],

@@ -1124,10 +1124,11 @@ def attention_scored(q, k_pool, v_pool, out, tok_seq, tok_pos, block_table, head
                int(maps), 1 if maps > 1 else 0, _p(gate), gs, vd, DT[q.dtype], _st(stream))
 
 
-def causal_conv(u, weight, bias, state, slots, tok_seq, seq_start, out, act: bool = False, stream=None) -> None:
+def causal_conv(u, weight, bias, state, slots, tok_seq, seq_start, out, act: bool = False, stream=None, max_count: int = 0) -> None:
     """out[t, c] = sum_j weight[c, j] * u_(t - taps + 1 + j)[c] (+ bias[c]; silu with ``act``) over each sequence's tokens
     of the step; inputs in front of the step come from ``state`` [slots, taps - 1, C] (the sequence's last inputs, zeros
-    at its start), which is then brought up to date. ``u`` and ``out`` are float32 rows, possibly views of wider ones."""
+    at its start), which is then brought up to date. ``u`` and ``out`` are float32 rows, possibly views of wider ones.
+    ``max_count``: the step's longest portion when known; steps of up to four tokens a sequence run as one launch."""
     _cuda(weight, bias, state, slots, tok_seq, seq_start)
     C, taps = weight.shape
     T = u.shape[0]
@@ -1136,7 +1137,7 @@ def causal_conv(u, weight, bias, state, slots, tok_seq, seq_start, out, act: boo
     _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (max(taps - 1, 0), C) or taps == 1, "causal_conv: state [slots, taps - 1, channels]")
     _need(out.shape[0] == T and slots.dtype == torch.int32 and tok_seq.dtype == torch.int32 and seq_start.dtype == torch.int32, "causal_conv: tables")
     lib().call("slb_causal_conv", _p(u), us, _p(weight), _p(bias), _p(state), _p(slots), _p(tok_seq), _p(seq_start), _p(out), os_,
-               T, slots.numel(), C, taps, 1 if act else 0, _st(stream))
+               T, slots.numel(), C, taps, 1 if act else 0, int(max_count), _st(stream))
 
 
 def decay_scan_scratch_floats(n_seqs: int, max_count: int, heads: int, N: int, P: int, per_channel: bool) -> int:

@@ -129,7 +129,7 @@ class StateSpace(Part):
         p = self.proj.forward(h, ws=ws, stream=b.stream, out_dtype=torch.float32)      # [z | x B C | dt]
         xbc = ws.take((T, inner + 2 * bc), torch.float32)
         tail = view["tail"].state if s.conv_taps > 1 else p[:0]
-        ops.causal_conv(p[:, inner:], self.conv_w, self.conv_b, tail, b.slots, b.tok_seq, b.seq_start, xbc, True, b.stream)
+        ops.causal_conv(p[:, inner:], self.conv_w, self.conv_b, tail, b.slots, b.tok_seq, b.seq_start, xbc, True, b.stream, max_count=b.max_count)
         dt, decay = ws.take((T, s.heads), torch.float32), ws.take((T, s.heads), torch.float32)
         ops.step_decay(p[:, 2 * inner + 2 * bc:], self.dt_bias, self.a_log, dt, decay, b.stream)
         y = ws.take((T, inner), torch.float32)

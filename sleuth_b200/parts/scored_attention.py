@@ -130,7 +130,7 @@ class ScoredAttention(Part):
         rows = p
         if self.conv is not None:
             rows = ws.take((T, nqkv), torch.float32)
-            ops.causal_conv(p, self.conv, None, view["tail"].state, b.slots, b.tok_seq, b.seq_start, rows, False, b.stream)
+            ops.causal_conv(p, self.conv, None, view["tail"].state, b.slots, b.tok_seq, b.seq_start, rows, False, b.stream, max_count=b.max_count)
         tables = self.position.tables()
         cos, sin = tables if tables is not None else (None, None)
         q = ws.take((T, s.heads * s.maps, self.pad or s.head_dim), dt)
