@@ -581,8 +581,9 @@ def fekitar_config(width, layers, heads, kv_heads, dim, window, state, lin_heads
                      "right": {"heads": heads, "vdim": dim, "state": state, "groups": 1, "conv": 4, "norm_groups": 1}}
             block.append({"type": "parallel", "mixer": mixer, "mlp": moe})
         else:
-            mixer = {"heads": heads // 2, "kv_heads": kv_heads // 2, "dim": dim, "vdim": 2 * dim, "scale": dim ** -0.5, "diff": 0.6, "conv": 3,
-                     "rot": {"base": 10000.0, "dims": dim}}
+            # two maps of 64 channels and values of 128 a head, whatever the other heads' width (as many heads as fill the width)
+            mixer = {"heads": heads * dim // 128, "kv_heads": max(1, kv_heads * dim // 128), "dim": 64, "vdim": 128, "scale": 0.125,
+                     "diff": 0.6, "conv": 3, "rot": {"base": 10000.0, "dims": 64}}
             if owner is not None:
                 mixer["kv_from"], owner = owner, None
             else:

@@ -53,6 +53,9 @@ struct AttnTcArgs {
   float scale_log2;
   int* status;
   const float* sinks;           // [H] or null: a learned score per head that joins the softmax denominator once, unscaled
+  // other score rules (off by default): score <- cap * tanh(score / cap), then score -= slopes[head] * (query position - key position)
+  float softcap_log2;           // cap * log2(e), or 0
+  const float* slopes;          // [H] or null
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -276,6 +279,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     unsigned short* xch = reinterpret_cast<unsigned short*>(smem + L::XCH_OFF);     // [2 pages][2 halves][128 rows]
     float m_used = -INFINITY, l = 0.0f;
+    // with a soft cap or a distance penalty the raw scores are turned into final ones (log2 units) right after they are read
+    const bool scored = a.softcap_log2 > 0.0f || a.slopes != nullptr;
+    const float sl2 = scored ? 1.0f : a.scale_log2;
+    const float slope_row = (a.slopes != nullptr && R < rows_total) ? a.slopes[kh * G + R % G] * 1.4426950408889634f : 0.0f;
     // A wait that gives up ends nothing here: the warp notes it, stops waiting and walks on to the end, because its
     // partner (the warp with the other half of the same rows) meets it at a hardware barrier twice per page and
     // would otherwise stay there. The result is then garbage and the status word says so.
@@ -298,6 +305,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       tc_fence_after();
       uint32_t sr[32];
       tmem_ld32(lane_addr + (uint32_t)(b * 64 + half * 32), sr);
+
+      if (scored) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float v = __uint_as_float(sr[c]) * a.scale_log2;
+          if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanhf(v / a.softcap_log2);
+          v -= slope_row * (float)(pos - (key0 + c));
+          sr[c] = __float_as_uint(v);
+        }
+      }
 
       // raw scores -> masked raw scores and their maximum; the mask costs two compares and a select per score, so
       // only warps with a row that needs it (the diagonal, a window's edge, padding) run it
@@ -323,7 +340,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const unsigned short other = xch[b * 256 + (half ^ 1) * 128 + r];
         mx = fmaxf(__uint_as_float((uint32_t)up << 16), __uint_as_float((uint32_t)other << 16));
       }
-      const float m_new = fmaxf(m_used, mx * a.scale_log2);               // the scale is positive
+      const float m_new = fmaxf(m_used, mx * sl2);               // the scale is positive
       const bool grow = m_new > m_used + kRescaleStep;      // also true for the first finite maximum
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         wait_warp(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 29);      // O must hold all of the last product
@@ -345,8 +362,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
-        const float p0 = ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_m));
-        const float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_m));
+        const float p0 = ex2(fmaf(__uint_as_float(sr[c]), sl2, neg_m));
+        const float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), sl2, neg_m));
         l0 += p0;
         l1 += p1;
         __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
@@ -592,6 +609,10 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     unsigned short* xch = reinterpret_cast<unsigned short*>(smem + L::XCH_OFF);     // [2 steps][4 parts][128 rows]
     float m_used = -INFINITY, l = 0.0f;
+    // with a soft cap or a distance penalty the raw scores are turned into final ones (log2 units) right after they are read
+    const bool scored = a.softcap_log2 > 0.0f || a.slopes != nullptr;
+    const float sl2 = scored ? 1.0f : a.scale_log2;
+    const float slope_row = (a.slopes != nullptr && R < rows_total) ? a.slopes[kh * G + R % G] * 1.4426950408889634f : 0.0f;
     bool ok = true;      // a wait that gives up ends nothing here, as in the kernel above
     auto wait_warp = [&](uint32_t bar, uint32_t parity, int code) {
       if (ok && !mbar_wait(bar, parity)) {
@@ -611,6 +632,16 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tc_fence_after();
       uint32_t sr[32];
       tmem_ld32(lane_addr + (uint32_t)(b * 128 + part * 32), sr);
+
+      if (scored) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float v = __uint_as_float(sr[c]) * a.scale_log2;
+          if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanhf(v / a.softcap_log2);
+          v -= slope_row * (float)(pos - (key0 + c));
+          sr[c] = __float_as_uint(v);
+        }
+      }
 
       // a page behind the tile's last one was never multiplied: what lies in its columns is masked like every key
       // behind the row's own position
@@ -633,7 +664,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mx = fmaxf(fmaxf(__uint_as_float((uint32_t)x[0] << 16), __uint_as_float((uint32_t)x[128] << 16)),
                    fmaxf(__uint_as_float((uint32_t)x[256] << 16), __uint_as_float((uint32_t)x[384] << 16)));
       }
-      const float m_new = fmaxf(m_used, mx * a.scale_log2);               // the scale is positive
+      const float m_new = fmaxf(m_used, mx * sl2);               // the scale is positive
       const bool grow = m_new > m_used + kRescaleStep;      // also true for the first finite maximum
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         wait_warp(pv_done + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 29);      // O must hold all of the last product
@@ -655,8 +686,8 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
-        const float p0 = ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_m));
-        const float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_m));
+        const float p0 = ex2(fmaf(__uint_as_float(sr[c]), sl2, neg_m));
+        const float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), sl2, neg_m));
         l0 += p0;
         l1 += p1;
         __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
@@ -780,11 +811,11 @@ extern "C" int slb_attention_tc_wide_pays(int n_seqs, int max_count, int max_key
 // all bfloat16. `status` is a zeroed device int that receives a code if a bounded wait inside the kernel gave up.
 // `wide`: 1 = the kernel that walks two pages a step, 0 = the one that walks one, -1 = chosen from the step's shape
 // (max_keys: the most keys a sequence has after this step, 0 if not known).
-extern "C" int slb_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const int* seq_start,
-                                const int* past, const int* counts, const int* block_table, int table_stride,
-                                int n_seqs, int max_count, long long tokens, long long pool_pages, int heads,
-                                int kv_heads, int head_dim, int window, float scale, int* status, int wide,
-                                int max_keys, const float* sinks, void* stream) {
+static int attention_tc_any(const void* q, const void* k_pool, const void* v_pool, void* out, const int* seq_start,
+                            const int* past, const int* counts, const int* block_table, int table_stride,
+                            int n_seqs, int max_count, long long tokens, long long pool_pages, int heads,
+                            int kv_heads, int head_dim, int window, float scale, int* status, int wide,
+                            int max_keys, const float* sinks, const float* slopes, float softcap, void* stream) {
   SLB_REQUIRE(slb_attention_tc_supported(heads, kv_heads, head_dim),
               "attention (tcgen05): heads=%d kv_heads=%d head_dim=%d is not taken (head size 64 or 128, group size a divisor of 128)",
               heads, kv_heads, head_dim);
@@ -818,7 +849,27 @@ extern "C" int slb_attention_tc(const void* q, const void* k_pool, const void* v
   a.out = (__nv_bfloat16*)out; a.seq_start = seq_start; a.past = past; a.counts = counts; a.block_table = block_table;
   a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f; a.status = status; a.sinks = sinks;
+  a.slopes = slopes; a.softcap_log2 = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
   const bool use_wide = wide < 0 ? wide_pays(n_seqs, max_count, max_keys, heads, kv_heads, window) : wide != 0;
   return head_dim == 64 ? launch_attn_tc<64>(mq, mk, mv, a, n_seqs, max_count, use_wide, (cudaStream_t)stream)
                         : launch_attn_tc<128>(mq, mk, mv, a, n_seqs, max_count, use_wide, (cudaStream_t)stream);
+}
+
+extern "C" int slb_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out, const int* seq_start,
+                                const int* past, const int* counts, const int* block_table, int table_stride,
+                                int n_seqs, int max_count, long long tokens, long long pool_pages, int heads,
+                                int kv_heads, int head_dim, int window, float scale, int* status, int wide,
+                                int max_keys, const float* sinks, void* stream) {
+  return attention_tc_any(q, k_pool, v_pool, out, seq_start, past, counts, block_table, table_stride, n_seqs, max_count, tokens,
+                          pool_pages, heads, kv_heads, head_dim, window, scale, status, wide, max_keys, sinks, nullptr, 0.0f, stream);
+}
+
+// The same kernels with a distance penalty per head (`slopes` [heads] or null) and a soft cap (0 = none) on the scores.
+extern "C" int slb_attention_tc_scored(const void* q, const void* k_pool, const void* v_pool, void* out, const int* seq_start,
+                                       const int* past, const int* counts, const int* block_table, int table_stride,
+                                       int n_seqs, int max_count, long long tokens, long long pool_pages, int heads,
+                                       int kv_heads, int head_dim, int window, float scale, int* status, int wide,
+                                       int max_keys, const float* slopes, float softcap, void* stream) {
+  return attention_tc_any(q, k_pool, v_pool, out, seq_start, past, counts, block_table, table_stride, n_seqs, max_count, tokens,
+                          pool_pages, heads, kv_heads, head_dim, window, scale, status, wide, max_keys, nullptr, slopes, softcap, stream);
 }

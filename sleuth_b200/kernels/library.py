@@ -171,6 +171,7 @@ _SIGNATURES = {
     "slb_gemm_tc_gated": [P, P, P, I, I, I, I, I, F, F, P, P],
     "slb_moe_experts": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
     "slb_attention_scored": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, F, I, I, P, L, I, I, P],
+    "slb_attention_tc_scored": [P, P, P, P, P, P, P, P, I, I, I, L, L, I, I, I, I, F, P, I, I, P, F, P],
     "slb_attention_prefill_scored": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, F, I, P],
     "slb_attention_decode_scored": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P, L, P, L, P, F, I, P],
     "slb_sigmoid_gate": [P, P, L, I, I, I, P],

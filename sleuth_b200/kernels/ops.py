@@ -399,13 +399,15 @@ def attention_tc_takes_two_pages(n_seqs: int, max_count: int, max_keys: int, hea
 
 def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
                  kv_heads: int, head_dim: int, window: int, scale: float, stream=None, wide: bool | None = None,
-                 max_keys: int = 0, sinks=None) -> None:
+                 max_keys: int = 0, sinks=None, slopes=None, softcap: float = 0.0) -> None:
     """Attention for a step in which sequences bring many tokens, on the tcgen05 tensor cores (same contract as
     ``attention_prefill``). A bounded wait that gave up inside the kernel shows in ``tc_check``. ``wide``: the
     kernel that walks two pages a step (True), one page a step (False), or the library's choice from the step's
-    shape; ``max_keys`` (the most keys a sequence has after this step, 0 = not known) helps that choice."""
-    _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table)
+    shape; ``max_keys`` (the most keys a sequence has after this step, 0 = not known) helps that choice. ``slopes`` /
+    ``softcap``: the score rules of ``attention_scored`` (not together with sinks)."""
+    _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table, slopes)
     _sinks_ok(sinks, heads)
+    _slopes_ok(slopes, heads, sinks)
     T, n = q.shape[0], block_table.shape[0]
     _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
     _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tcgen05): bfloat16 only")
@@ -413,6 +415,12 @@ def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, m
           "attention (tcgen05): contiguous tensors")
     _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
     _need(seq_start.numel() >= n + 1 and past.numel() >= n and counts.numel() >= n, "attention: per-sequence tables")
+    if slopes is not None or softcap:
+        lib().call("slb_attention_tc_scored", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
+                   _p(block_table), block_table.shape[1], n, int(max_count), T, k_pool.shape[0], heads, kv_heads, head_dim,
+                   int(window), float(scale), _p(_tc_status(q.device)), -1 if wide is None else int(bool(wide)),
+                   int(max_keys), _p(slopes), float(softcap), stream if stream is not None else current_stream())
+        return
     lib().call("slb_attention_tc", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
                _p(block_table), block_table.shape[1], n, int(max_count), T, k_pool.shape[0], heads, kv_heads, head_dim,
                int(window), float(scale), _p(_tc_status(q.device)), -1 if wide is None else int(bool(wide)),

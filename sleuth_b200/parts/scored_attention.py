@@ -4,7 +4,9 @@ One stacked projection [q | k | v | gate] with a float32 result; then, as the sp
 time on the q, k and v channels (``ops.causal_conv``; a sequence's last taps - 1 projected values are state); per-unit RMS
 norm, rotation and the cache write (``ops.unit_post``); attention over the paged cache by the general kernel with a soft
 cap, a distance penalty per head, a window, and one or two score maps a head (``ops.attention_scored``); for two maps the
-difference a1 - lambda a2 with its norm and the head gates (``ops.diff_combine``); the output projection into the stream.
+difference a1 - lambda a2 with its norm and the head gates (``ops.diff_combine``); the output projection into the stream. In bfloat16, one map with keys and values of 64 or 128 channels runs on the
+tensor-core kernels instead (tcgen05 for steps that fill its 128-row tiles, mma.sync otherwise and for single tokens), and
+two maps whose rows fit 128 channels run on the mma.sync kernels over rows widened with zero channels.
 
 The entry keeps keys and values in pages (a key row is ``maps * head_dim`` wide, so both maps' keys of a position lie
 together) and, with a convolution, the tails of the projected rows per sequence. A part that ``reads_shared_kv`` has no key
@@ -19,6 +21,7 @@ import torch
 
 from ..cache.paged import BundleRequest, KVRequest, StateRequest
 from ..kernels import ops
+from .attention import use_tc_attention
 from .base import BuildContext, Normed, ParamDecl, Part, build_position, register_mixer, result_target
 from .linear import Linear
 from .spec import ScoredAttentionSpec
@@ -147,6 +150,10 @@ class ScoredAttention(Part):
                 ops.attention_decode(q, kv.k_pool, kv.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads, s.head_dim,
                                      kv.window, self.scale, splits, scratch, b.stream, next_read=self.o.weight, slopes=self.slopes,
                                      softcap=s.softcap)
+            elif use_tc_attention(s.heads, s.kv_heads, s.head_dim, dt, b.max_count, self.scale):
+                ops.attention_tc(q, kv.k_pool, kv.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count, s.heads,
+                                 s.kv_heads, s.head_dim, kv.window, self.scale, b.stream, max_keys=b.max_len, slopes=self.slopes,
+                                 softcap=s.softcap)
             else:
                 ops.attention_prefill(q, kv.k_pool, kv.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count, s.heads,
                                       s.kv_heads, s.head_dim, kv.window, self.scale, b.stream, slopes=self.slopes, softcap=s.softcap)

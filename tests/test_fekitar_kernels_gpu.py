@@ -252,7 +252,10 @@ def attention_case(o, dtype, H, G, d, dv, maps, lengths, pasts, window, slopes, 
             _, _, start = batch_tables(counts_live)
             past_d, counts_d = i32([begin[i] for i in live]), i32(counts_live)
             sl = None if slopes is None else slopes.to(DEV)
-            if max(counts_live) == 1:
+            if flash == "tc" and max(counts_live) > 1:      # the tcgen05 kernels (one page a step and two pages a step in turn)
+                o.attention_tc(q, k_pool, v_pool, out.view(T, -1), start, past_d, counts_d, tab, max(counts_live), H, G, d, window, 0.3,
+                               wide=bool(len(lengths) % 2), max_keys=max(lengths), slopes=sl, softcap=softcap)
+            elif max(counts_live) == 1:
                 splits = 3
                 scratch = torch.empty(o.decode_scratch_floats(len(live), H, d, splits), device=DEV)
                 o.attention_decode(q, k_pool, v_pool, out.view(T, -1), start, past_d, tab, H, G, d, window, 0.3, splits, scratch,
@@ -319,20 +322,23 @@ def test_far_keys_soft_caps_rotation_and_two_maps(H, G, d, dv, maps, rot, softca
             torch.testing.assert_close(a.double(), b, **tol)
 
 
+@pytest.mark.parametrize("path", [True, "tc"])
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("window,softcap", [(0, 5.0), (37, 0.0), (64, 0.0), (130, 3.0), (0, 0.0)])
-def test_the_tensor_core_kernels_know_the_penalty_and_the_cap(d, window, softcap):
-    """The mma.sync prompt and single-token kernels with a distance penalty a head, a soft cap and a window: a loud key
-    just inside and just outside the window (or far back without one), in whole prompts, portions and single tokens."""
+def test_the_tensor_core_kernels_know_the_penalty_and_the_cap(d, window, softcap, path):
+    """The mma.sync prompt and single-token kernels and the two tcgen05 prompt kernels with a distance penalty a head, a soft
+    cap and a window: a loud key just inside and just outside the window (or far back without one), in whole prompts,
+    portions and single tokens."""
     o = ops()
     H, G = 8, 2
     slopes = plain.distance_slopes(H, torch.float32) if softcap != 5.0 else None
     tol = dict(rtol=3e-2, atol=3e-2)
     for loud in ((window - 1, window) if window else (300,)):
         for lengths, pasts in (([window + 270, 200, 3], [0, 0, 0]), ([window + 270, 200, 70], [window + 269, 199, 69]), ([window + 270, 150], [100, 64])):
-            got, want = attention_case(o, torch.bfloat16, H, G, d, d, 1, lengths, pasts, window, slopes, softcap, d, True, loud, flash=True)
+            got, want = attention_case(o, torch.bfloat16, H, G, d, d, 1, lengths, pasts, window, slopes, softcap, d, True, loud, flash=path)
             for a, b in zip(got, want):
                 torch.testing.assert_close(a.double(), b, **tol)
+    o.gemm_tc_check(torch.device(DEV))          # no bounded wait inside a tensor-memory kernel gave up
 
 
 @pytest.mark.parametrize("H,G,d,dv,rot,pad", [(2, 1, 16, 40, 8, 64), (4, 2, 32, 64, 32, 64), (4, 1, 48, 96, 48, 128), (3, 3, 8, 16, 0, 64),
