@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
         for (int e = 0; e < 4; ++e) {
           const int h = e >> 1;
           float v = s[j][e] * a.scale_log2;
-          if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanhf(v / a.softcap_log2);
+          if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanh_ex2(v / a.softcap_log2);
           if (a.slopes != nullptr) v -= slope_r[h] * (float)(pos_r[h] - (key0 + j * 8 + 2 * t4 + (e & 1)));
           if (need_mask) {
             const int key = key0 + j * 8 + 2 * t4 + (e & 1);
@@ -508,7 +508,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
           for (int e = 0; e < 4; ++e) {
             const int key = key0 + j * 8 + 2 * t4 + (e & 1);
             float v = s[j][e] * a.scale_log2;
-            if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanhf(v / a.softcap_log2);
+            if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanh_ex2(v / a.softcap_log2);
             if (a.slopes != nullptr) v -= slope_r[e >> 1] * (float)(pos - key);
             if (key > pos || key < key_lo) v = -INFINITY;
             s[j][e] = v;

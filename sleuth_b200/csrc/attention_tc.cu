@@ -310,7 +310,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
           float v = __uint_as_float(sr[c]) * a.scale_log2;
-          if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanhf(v / a.softcap_log2);
+          if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanh_ex2(v / a.softcap_log2);
           v -= slope_row * (float)(pos - (key0 + c));
           sr[c] = __float_as_uint(v);
         }
@@ -637,7 +637,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
           float v = __uint_as_float(sr[c]) * a.scale_log2;
-          if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanhf(v / a.softcap_log2);
+          if (a.softcap_log2 > 0.0f) v = a.softcap_log2 * tanh_ex2(v / a.softcap_log2);
           v -= slope_row * (float)(pos - (key0 + c));
           sr[c] = __float_as_uint(v);
         }

@@ -227,6 +227,15 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// tanh through one exponential and one division of the fast units: 1 - 2 / (2^(2 x log2 e) + 1). Absolute error about
+// 2e-7 over the whole range (the ends come out as exactly -1 and 1), which is what a soft cap in a score loop needs;
+// tanhf costs several times as much there.
+__device__ __forceinline__ float tanh_ex2(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+
 // Sum over a block of up to 1024 threads; every thread gets the result. `scratch` holds 33 floats.
 // The order of additions is fixed by the thread layout, so a row's sum never depends on what else runs.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {

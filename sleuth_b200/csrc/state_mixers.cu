@@ -230,11 +230,25 @@ __global__ void __launch_bounds__(256) scan_starts_kernel(ScanArgs a, const floa
   const int count = a.seq_start[seq + 1] - a.seq_start[seq];
   float* st = a.state + (size_t)a.slots[seq] * per_seq + r;
   float s = *st;
-  for (int c = 0; c < a.chunks && c * a.chunk_len < count; ++c) {
-    float* e = a.starts + ((size_t)seq * a.chunks + c) * per_seq + r;
-    const float end = *e;
-    *e = s;
-    s = fmaf(prod[(((size_t)seq * a.chunks + c) * a.heads + h) * Nn + (a.a_per_channel ? n : 0)], s, end);
+  const int live = min(a.chunks, (count + a.chunk_len - 1) / a.chunk_len);      // chunks that hold tokens
+  float* e = a.starts + (size_t)seq * a.chunks * per_seq + r;
+  const float* pr = prod + ((size_t)seq * a.chunks * a.heads + h) * Nn + (a.a_per_channel ? n : 0);
+  // eight chunks' end states and decay products are asked for before the dependent chain of eight updates runs
+  for (int c0 = 0; c0 < live; c0 += 8) {
+    float end[8], dec[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool in = c0 + j < live;
+      end[j] = in ? e[(size_t)(c0 + j) * per_seq] : 0.0f;
+      dec[j] = in ? pr[(size_t)(c0 + j) * a.heads * Nn] : 1.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (c0 + j < live) {
+        e[(size_t)(c0 + j) * per_seq] = s;
+        s = fmaf(dec[j], s, end[j]);
+      }
+    }
   }
   *st = s;
 }
