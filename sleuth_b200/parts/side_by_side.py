@@ -2,6 +2,10 @@
 kernel joins the two results into the stream (``SideBySideSpec``): half the sum of the two after an RMS norm each with a
 gain of its own, or a weighted sum. The pair's cache entry is a bundle of the two mixers' requests, so an attention's
 pages and a recurrence's state of one layer are taken, freed and reused together.
+
+The two mixers need nothing from each other. In a step that brings one token a sequence, where each is a chain of short
+kernels that wait for one another, the right one runs on a second stream beside the left one (as a parallel layer's
+feed-forward does, ``parts/layer.py``); recorded steps keep the fork and the join. SLEUTH_B200_BRANCH=0 turns it off.
 """
 
 from __future__ import annotations
@@ -11,6 +15,7 @@ import torch
 from ..cache.paged import BundleRequest
 from ..kernels import ops
 from .base import BuildContext, Normed, ParamDecl, Part, build_mixer, lead_weight_of, register_mixer
+from .layer import BRANCH, _side_stream
 from .spec import SideBySideSpec
 
 
@@ -58,9 +63,11 @@ class SideBySide(Part):
         b.store_first = False
         after = getattr(b, "next_read", None)
         mark = ws.mark()
-        results = []
-        for name, part, following in (("left", self.left, lead_weight_of(self.right)), ("right", self.right, after)):
-            y = ws.take(x.shape, torch.float32)
+        results = [ws.take(x.shape, torch.float32), ws.take(x.shape, torch.float32)]
+        branch = BRANCH and b.max_count == 1 and x.is_cuda
+
+        def run(i, name, part, following):
+            y = results[i]
             if getattr(part, "stores_result", False):
                 b.store_first = True
             else:
@@ -73,7 +80,24 @@ class SideBySide(Part):
             part.forward(h, y, b, sub, ws)
             if getattr(b, "store_first", False):
                 raise RuntimeError(f"{type(part).__name__} says it stores its result and did not")
-            results.append(y)
+
+        if branch:
+            # the right mixer on a second stream; its scratch memory is taken first, and the left one's begins above the
+            # highest address it used, so the two never share a byte
+            main, side = torch.cuda.current_stream(), _side_stream(x.device)
+            seen, ws.high = ws.high, ws.top
+            side.wait_stream(main)              # the normed input is ready
+            with torch.cuda.stream(side):
+                b.stream = side.cuda_stream
+                run(1, "right", self.right, None)
+            b.stream = main.cuda_stream
+            ws.top = max(ws.top, ws.high)
+            ws.high = max(seen, ws.high)
+            run(0, "left", self.left, None)
+            main.wait_stream(side)
+        else:
+            run(0, "left", self.left, lead_weight_of(self.right))
+            run(1, "right", self.right, after)
         b.next_read = after
         if s.combine == "normed_mean":
             ops.pair_combine(results[0], results[1], x, self.gain_left, self.gain_right, 0.5, 0.5, s.eps, accumulate=not store,

@@ -131,15 +131,15 @@ def test_window_membership_and_the_distance_penalty():
 
 def test_frequency_rescaling_band_by_band():
     from sleuth_b200.parts.position import rescale_bands
-    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 512}}
+    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 6.0, "low": 2.0, "high": 5.0, "original": 640}}
     plain_f = plain.rotary_frequencies(rot, torch.float64)
     base = 10000.0 ** (-torch.arange(32, dtype=torch.float64) * 2 / 64)
-    torch.testing.assert_close(rescale_bands(base, 8.0, 1.0, 4.0, 512), plain_f)
+    torch.testing.assert_close(rescale_bands(base, 6.0, 2.0, 5.0, 640), plain_f)
     wavelength = 2 * torch.pi / base
     assert torch.equal(plain_f[wavelength < 128], base[wavelength < 128])
-    assert torch.allclose(plain_f[wavelength > 512], base[wavelength > 512] / 8.0)
-    between = (wavelength >= 128) & (wavelength <= 512)
-    assert between.any() and bool(((plain_f[between] <= base[between]) & (plain_f[between] >= base[between] / 8.0)).all())
+    assert torch.allclose(plain_f[wavelength > 320], base[wavelength > 320] / 6.0)
+    between = (wavelength >= 128) & (wavelength <= 320)
+    assert between.any() and bool(((plain_f[between] <= base[between]) & (plain_f[between] >= base[between] / 6.0)).all())
 
 
 def test_routing_weights_sum_to_one_and_the_shared_expert_is_gated():
