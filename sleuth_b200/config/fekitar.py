@@ -170,7 +170,7 @@ class FekitarConfig:
 
         need(self.vocab > 0 and self.width > 0, f"vocab ({self.vocab}) and width ({self.width}) must be positive")
         need(len(self.layers) > 0, "layers is empty")
-        need(0 <= self.streams <= 8, f"streams must lie in 0..8, got {self.streams}")
+        need(0 <= self.streams <= 16, f"streams must lie in 0..16, got {self.streams}")
         object.__setattr__(self, "eps", _strict(_Norm, self.norm, "config.json: norm").eps)
         need(self.eps > 0, f"norm.eps must be positive, got {self.eps}")
         parsed = []

@@ -14,7 +14,7 @@
 
 namespace slb {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;
 
 __global__ void __launch_bounds__(256) streams_fill_kernel(const float* __restrict__ x0, float* __restrict__ xs, long long rows,
                                                            int d, int S) {
@@ -104,7 +104,9 @@ __global__ void __launch_bounds__(256) hyper_read_vec_kernel(const float* __rest
   }
 }
 
-// One thread per (token, four channels): the same arithmetic as hyper_write_kernel with 16-byte loads and stores.
+// One thread per (token, four channels): the same arithmetic as hyper_write_kernel with 16-byte loads and stores. MAXS: the
+// most copies this instance holds in registers (4, 8 or 16), so that few copies do not pay for the registers of many.
+template <int MAXS>
 __global__ void __launch_bounds__(256) hyper_write_vec_kernel(float* __restrict__ xs, const float* __restrict__ y,
                                                               const float* __restrict__ mix, const float* __restrict__ out_coef,
                                                               long long rows, int d, int S, float mult) {
@@ -115,18 +117,18 @@ __global__ void __launch_bounds__(256) hyper_write_vec_kernel(float* __restrict_
   const long long t = i / d4;
   const int c = (int)(i - t * d4);
   float4* base = reinterpret_cast<float4*>(xs + (size_t)t * S * d) + c;
-  float4 old[kMaxStreams];
+  float4 old[MAXS];
 #pragma unroll
-  for (int s = 0; s < kMaxStreams; ++s) old[s] = s < S ? base[(size_t)s * d4] : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < MAXS; ++s) old[s] = s < S ? base[(size_t)s * d4] : make_float4(0.f, 0.f, 0.f, 0.f);
   float4 yv = reinterpret_cast<const float4*>(y)[i];
   yv.x *= mult; yv.y *= mult; yv.z *= mult; yv.w *= mult;
 #pragma unroll
-  for (int r = 0; r < kMaxStreams; ++r) {
+  for (int r = 0; r < MAXS; ++r) {
     if (r < S) {
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (mix) {
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s) {
+        for (int s = 0; s < MAXS; ++s) {
           if (s < S) {
             const float m = mix[s * S + r];
             v.x = fmaf(m, old[s].x, v.x);
@@ -284,10 +286,13 @@ extern "C" int slb_hyper_write(float* xs, const float* y, const float* mix, cons
   SLB_REQUIRE(rows >= 0 && d > 0 && S >= 1 && S <= kMaxStreams, "hyper_write: rows=%lld d=%d streams=%d (at most %d)", rows, d, S,
               kMaxStreams);
   if (rows == 0) return 0;
-  if (d % 4 == 0 && (uintptr_t)xs % 16 == 0 && (uintptr_t)y % 16 == 0)
-    launch(hyper_write_vec_kernel, per_element(rows * (d / 4)), dim3(256), 0, (cudaStream_t)stream, xs, y, mix, out_coef, rows, d, S, mult);
-  else
+  if (d % 4 == 0 && (uintptr_t)xs % 16 == 0 && (uintptr_t)y % 16 == 0) {
+    if (S <= 4) launch(hyper_write_vec_kernel<4>, per_element(rows * (d / 4)), dim3(256), 0, (cudaStream_t)stream, xs, y, mix, out_coef, rows, d, S, mult);
+    else if (S <= 8) launch(hyper_write_vec_kernel<8>, per_element(rows * (d / 4)), dim3(256), 0, (cudaStream_t)stream, xs, y, mix, out_coef, rows, d, S, mult);
+    else launch(hyper_write_vec_kernel<16>, per_element(rows * (d / 4)), dim3(256), 0, (cudaStream_t)stream, xs, y, mix, out_coef, rows, d, S, mult);
+  } else {
     launch(hyper_write_kernel, per_element(rows * d), dim3(256), 0, (cudaStream_t)stream, xs, y, mix, out_coef, rows, d, S, mult);
+  }
   return check_launch("hyper_write");
 }
 

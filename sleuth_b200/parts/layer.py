@@ -268,8 +268,8 @@ class HyperLayer(Part):
         for name, part in self.children.items():
             if name.startswith("norm") and not getattr(part, "fusable", False):
                 raise ValueError("hyper layer: its norms must be RMS norms")
-        if self.streams > 8:
-            raise ValueError(f"hyper layer: at most 8 copies of the stream, got {self.streams}")
+        if self.streams > 16:
+            raise ValueError(f"hyper layer: at most 16 copies of the stream, got {self.streams}")
         self.coef = {}
         self.capturable = all(getattr(p, "capturable", True) for p in self.children.values())
 

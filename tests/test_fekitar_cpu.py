@@ -93,7 +93,7 @@ def test_refusals():
     broken(lambda c: c["layers"][4]["mixer"].update(vdim=8))                          # other widths than its lender's
     broken(lambda c: c["layers"][2]["mixer"].pop("diff"))
     broken(lambda c: c["layers"][1]["mlp"]["router"].update(top=7))
-    broken(lambda c: c.update(streams=9))
+    broken(lambda c: c.update(streams=17))
     broken(lambda c: c["layers"][0]["mixer"]["right"].update(groups=2))               # 3 heads in 2 groups
 
 

@@ -371,7 +371,7 @@ def test_differential_combination(dtype):
 
 # ---------------------------------------------------------------- copies of the stream, joins, gates ----
 
-@pytest.mark.parametrize("S,d", [(1, 40), (3, 72), (4, 320), (8, 33)])
+@pytest.mark.parametrize("S,d", [(1, 40), (3, 72), (4, 320), (8, 33), (16, 64)])
 def test_copies_of_the_stream(S, d):
     o = ops()
     g = torch.Generator().manual_seed(S * 7 + d)
